@@ -1,0 +1,24 @@
+/*
+ * conv_kernels.hpp -- launchers of the tensor-core convolution kernels.
+ *
+ * Each returns AVOCADO_STATUS_NOT_SUPPORTED, without launching anything, when the shape, dtype or alignment is
+ * outside what the kernel covers; the caller then uses the direct CUDA-core kernel.
+ */
+#ifndef B200_CONV_KERNELS_HPP_
+#define B200_CONV_KERNELS_HPP_
+
+#include "objects.hpp"
+#include "conv_common.cuh"
+
+namespace bk
+{
+	/* implicit-GEMM convolution on tcgen05 (int8 with int32 accumulation; float16 / bfloat16 with float32 accumulation) */
+	avocado::backend::avStatus_t launch_implicit_gemm_tc(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
+			avocado::backend::avDataType_t xType, avocado::backend::avDataType_t yType, const void *alpha1, const void *alpha2, const void *beta);
+
+	/* fused Winograd F(2x2,3x3) forward on tcgen05 */
+	avocado::backend::avStatus_t launch_winograd_fused_tc(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
+			avocado::backend::avDataType_t xType, avocado::backend::avDataType_t yType, const void *alpha1, const void *alpha2, const void *beta);
+} /* namespace bk */
+
+#endif /* B200_CONV_KERNELS_HPP_ */

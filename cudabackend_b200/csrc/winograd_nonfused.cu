@@ -1,0 +1,711 @@
+/*
+ * winograd_nonfused.cu -- the five tile transforms of the non-fused Winograd pipeline.
+ *
+ * Entry points and their reference counterparts (src/winograd_nonfused.cu):
+ *   cudaWinogradWeightTransform   :881  kernel :256   w[K,k,k,C]        -> U[t*t, K, C]
+ *   cudaWinogradInputTransform    :906  kernel :302   x[N,H,W,C]        -> V[t*t, tiles, C]
+ *   cudaWinogradOutputTransform   :932  kernel :366   M[t*t, tiles, K]  -> y[N,H,W,K]  (+ bias, z, activation, beta)
+ *   cudaWinogradGradientTransform :963  kernel :424   dy[N,H,W,K]       -> [t*t, tiles, K]
+ *   cudaWinogradUpdateTransform   :983  kernel :476   [t*t, K, C]       -> dw[K,k,k,C]
+ *
+ * All five are bandwidth-bound.  One thread owns one tile (or one filter) for VEC adjacent channels: the
+ * channel index is the fastest-varying thread index, so every load and store of a warp is one contiguous
+ * run of VEC * 32 channels, and all loads of a tile are issued before the first use.  Arithmetic is float
+ * (double for float64 tensors) with one rounding on store.  The transform-domain tensor may be float32 while
+ * the activations are 16-bit, which is what keeps F(4x4,3x3) within 1e-2 of an exact convolution.
+ */
+#include <Avocado/cuda_backend.h>
+
+#include "objects.hpp"
+#include "device_utils.cuh"
+#include "winograd_tables.cuh"
+
+#include <cuda_runtime_api.h>
+
+namespace
+{
+	using namespace avocado::backend;
+	using namespace avocado::backend::b200;
+	using namespace ::bk;
+	using winograd::Transform;
+	using winograd::Matrix;
+
+	constexpr int kThreads = 256;
+
+	struct ConvGeometry
+	{
+			int batch, height, width, channels; /* of the NHWC tensor being tiled */
+			int tiles_h, tiles_w;
+			int pad_h, pad_w;
+			__host__ __device__ long long nb_tiles() const
+			{
+				return static_cast<long long>(batch) * tiles_h * tiles_w;
+			}
+	};
+
+	template<int TS, int KS, typename T, typename MT, int VEC>
+	__global__ void __launch_bounds__(kThreads) kernel_weight_transform(MT *__restrict__ matrices, const T *__restrict__ weights, int filtersOut,
+			int filtersIn, bool invert)
+	{
+		using CT = typename ComputeType<T>::type;
+		using M = Matrix<Transform::Weight, TS, KS>;
+		const int cvecs = filtersIn / VEC;
+		const long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+		if (g >= static_cast<long long>(filtersOut) * cvecs)
+			return;
+		const int c0 = static_cast<int>(g % cvecs) * VEC;
+		const int k = static_cast<int>(g / cvecs);
+
+		CT in[VEC][KS * KS];
+#pragma unroll
+		for (int i = 0; i < KS * KS; i++)
+		{
+			const Vec<T, VEC> tmp = load_vec<T, VEC>(weights + (static_cast<size_t>(k) * KS * KS + i) * filtersIn + c0);
+			const int dst = invert ? (KS * KS - 1 - i) : i; /* 180 degree rotation of the kernel */
+#pragma unroll
+			for (int v = 0; v < VEC; v++)
+				in[v][dst] = to_compute(tmp.v[v]);
+		}
+		CT out[VEC][M::Rows * M::Rows];
+#pragma unroll
+		for (int v = 0; v < VEC; v++)
+			winograd::transform_2d<M, CT>(in[v], out[v]);
+#pragma unroll
+		for (int p = 0; p < M::Rows * M::Rows; p++)
+		{
+			Vec<MT, VEC> tmp;
+#pragma unroll
+			for (int v = 0; v < VEC; v++)
+				tmp.v[v] = from_compute<MT>(out[v][p]);
+			store_vec<MT, VEC>(matrices + (static_cast<size_t>(p) * filtersOut + k) * filtersIn + c0, tmp);
+		}
+	}
+
+	template<int TS, int KS, typename T, typename MT, int VEC>
+	__global__ void __launch_bounds__(kThreads) kernel_input_transform(MT *__restrict__ matrices, const T *__restrict__ input, ConvGeometry geo,
+			typename ComputeType<T>::type paddingValue)
+	{
+		using CT = typename ComputeType<T>::type;
+		using M = Matrix<Transform::Input, TS, KS>;
+		constexpr int TL = M::Tile;
+		const int cvecs = geo.channels / VEC;
+		const long long nb_tiles = geo.nb_tiles();
+		const long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+		if (g >= nb_tiles * cvecs)
+			return;
+		const int c0 = static_cast<int>(g % cvecs) * VEC;
+		const long long tile = g / cvecs;
+		const int tw = static_cast<int>(tile % geo.tiles_w);
+		const int th = static_cast<int>((tile / geo.tiles_w) % geo.tiles_h);
+		const int n = static_cast<int>(tile / (static_cast<long long>(geo.tiles_w) * geo.tiles_h));
+
+		CT in[VEC][TL * TL];
+#pragma unroll
+		for (int r = 0; r < TL; r++)
+		{
+			const int h = geo.pad_h + th * TS + r;
+#pragma unroll
+			for (int c = 0; c < TL; c++)
+			{
+				const int w = geo.pad_w + tw * TS + c;
+				if (h >= 0 and h < geo.height and w >= 0 and w < geo.width)
+				{
+					const Vec<T, VEC> tmp = load_vec<T, VEC>(input + ((static_cast<size_t>(n) * geo.height + h) * geo.width + w) * geo.channels + c0);
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						in[v][r * TL + c] = to_compute(tmp.v[v]);
+				}
+				else
+				{
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						in[v][r * TL + c] = paddingValue;
+				}
+			}
+		}
+		CT out[VEC][TL * TL];
+#pragma unroll
+		for (int v = 0; v < VEC; v++)
+			winograd::transform_2d<M, CT>(in[v], out[v]);
+#pragma unroll
+		for (int p = 0; p < TL * TL; p++)
+		{
+			Vec<MT, VEC> tmp;
+#pragma unroll
+			for (int v = 0; v < VEC; v++)
+				tmp.v[v] = from_compute<MT>(out[v][p]);
+			store_vec<MT, VEC>(matrices + (static_cast<size_t>(p) * nb_tiles + tile) * geo.channels + c0, tmp);
+		}
+	}
+
+	template<int TS, int KS, typename T, typename MT, int VEC>
+	__global__ void __launch_bounds__(kThreads) kernel_gradient_transform(MT *__restrict__ matrices, const T *__restrict__ gradient, ConvGeometry geo)
+	{
+		using CT = typename ComputeType<T>::type;
+		using M = Matrix<Transform::Gradient, TS, KS>;
+		constexpr int TL = M::Tile;
+		const int cvecs = geo.channels / VEC;
+		const long long nb_tiles = geo.nb_tiles();
+		const long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+		if (g >= nb_tiles * cvecs)
+			return;
+		const int c0 = static_cast<int>(g % cvecs) * VEC;
+		const long long tile = g / cvecs;
+		const int tw = static_cast<int>(tile % geo.tiles_w);
+		const int th = static_cast<int>((tile / geo.tiles_w) % geo.tiles_h);
+		const int n = static_cast<int>(tile / (static_cast<long long>(geo.tiles_w) * geo.tiles_h));
+
+		CT in[VEC][TS * TS];
+#pragma unroll
+		for (int r = 0; r < TS; r++)
+		{
+			const int h = th * TS + r;
+#pragma unroll
+			for (int c = 0; c < TS; c++)
+			{
+				const int w = tw * TS + c;
+				if (h < geo.height and w < geo.width)
+				{
+					const Vec<T, VEC> tmp = load_vec<T, VEC>(gradient + ((static_cast<size_t>(n) * geo.height + h) * geo.width + w) * geo.channels + c0);
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						in[v][r * TS + c] = to_compute(tmp.v[v]);
+				}
+				else
+				{
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						in[v][r * TS + c] = static_cast<CT>(0);
+				}
+			}
+		}
+		CT out[VEC][TL * TL];
+#pragma unroll
+		for (int v = 0; v < VEC; v++)
+			winograd::transform_2d<M, CT>(in[v], out[v]);
+#pragma unroll
+		for (int p = 0; p < TL * TL; p++)
+		{
+			Vec<MT, VEC> tmp;
+#pragma unroll
+			for (int v = 0; v < VEC; v++)
+				tmp.v[v] = from_compute<MT>(out[v][p]);
+			store_vec<MT, VEC>(matrices + (static_cast<size_t>(p) * nb_tiles + tile) * geo.channels + c0, tmp);
+		}
+	}
+
+	/* BT is the bias type: float for 16-bit and float32 tensors, double for float64
+	 * (ref src/winograd_nonfused.cu:758, :944-958). */
+	template<int TS, int KS, typename T, typename MT, typename BT, int VEC>
+	__global__ void __launch_bounds__(kThreads) kernel_output_transform(const MT *__restrict__ matrices, T *output, ConvGeometry geo,
+			const BT *__restrict__ bias, const T *__restrict__ ext, typename ComputeType<T>::type alpha1, typename ComputeType<T>::type alpha2,
+			typename ComputeType<T>::type beta, avActivationType_t activation)
+	{
+		using CT = typename ComputeType<T>::type;
+		using M = Matrix<Transform::Output, TS, KS>;
+		constexpr int TL = M::Tile;
+		const int cvecs = geo.channels / VEC;
+		const long long nb_tiles = geo.nb_tiles();
+		const long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+		if (g >= nb_tiles * cvecs)
+			return;
+		const int c0 = static_cast<int>(g % cvecs) * VEC;
+		const long long tile = g / cvecs;
+		const int tw = static_cast<int>(tile % geo.tiles_w);
+		const int th = static_cast<int>((tile / geo.tiles_w) % geo.tiles_h);
+		const int n = static_cast<int>(tile / (static_cast<long long>(geo.tiles_w) * geo.tiles_h));
+
+		CT in[VEC][TL * TL];
+#pragma unroll
+		for (int p = 0; p < TL * TL; p++)
+		{
+			const Vec<MT, VEC> tmp = load_vec<MT, VEC>(matrices + (static_cast<size_t>(p) * nb_tiles + tile) * geo.channels + c0);
+#pragma unroll
+			for (int v = 0; v < VEC; v++)
+				in[v][p] = static_cast<CT>(to_compute(tmp.v[v]));
+		}
+		CT out[VEC][TS * TS];
+#pragma unroll
+		for (int v = 0; v < VEC; v++)
+			winograd::transform_2d<M, CT>(in[v], out[v]);
+
+		CT b[VEC];
+#pragma unroll
+		for (int v = 0; v < VEC; v++)
+			b[v] = (bias != nullptr) ? static_cast<CT>(bias[c0 + v]) : static_cast<CT>(0);
+
+#pragma unroll
+		for (int r = 0; r < TS; r++)
+		{
+			const int h = th * TS + r;
+#pragma unroll
+			for (int c = 0; c < TS; c++)
+			{
+				const int w = tw * TS + c;
+				if (h < geo.height and w < geo.width)
+				{
+					const size_t index = ((static_cast<size_t>(n) * geo.height + h) * geo.width + w) * geo.channels + c0;
+					CT val[VEC];
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						val[v] = alpha1 * out[v][r * TS + c] + b[v];
+					if (ext != nullptr)
+					{
+						const Vec<T, VEC> tmp = load_vec<T, VEC>(ext + index);
+#pragma unroll
+						for (int v = 0; v < VEC; v++)
+							val[v] += alpha2 * to_compute(tmp.v[v]);
+					}
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						val[v] = activation_forward(activation, val[v]);
+					if (beta != static_cast<CT>(0))
+					{
+						const Vec<T, VEC> tmp = load_vec<T, VEC>(output + index);
+#pragma unroll
+						for (int v = 0; v < VEC; v++)
+							val[v] += beta * to_compute(tmp.v[v]);
+					}
+					Vec<T, VEC> result;
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+						result.v[v] = from_compute<T>(val[v]);
+					store_vec<T, VEC>(output + index, result);
+				}
+			}
+		}
+	}
+
+	template<int TS, int KS, typename T, int VEC>
+	__global__ void __launch_bounds__(kThreads) kernel_update_transform(const T *__restrict__ matrices, T *update, int filtersOut, int filtersIn,
+			typename ComputeType<T>::type alpha, typename ComputeType<T>::type beta)
+	{
+		using CT = typename ComputeType<T>::type;
+		using M = Matrix<Transform::Update, TS, KS>;
+		constexpr int TL = M::Tile;
+		const int cvecs = filtersIn / VEC;
+		const long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+		if (g >= static_cast<long long>(filtersOut) * cvecs)
+			return;
+		const int c0 = static_cast<int>(g % cvecs) * VEC;
+		const int k = static_cast<int>(g / cvecs);
+
+		CT in[VEC][TL * TL];
+#pragma unroll
+		for (int p = 0; p < TL * TL; p++)
+		{
+			const Vec<T, VEC> tmp = load_vec<T, VEC>(matrices + (static_cast<size_t>(p) * filtersOut + k) * filtersIn + c0);
+#pragma unroll
+			for (int v = 0; v < VEC; v++)
+				in[v][p] = to_compute(tmp.v[v]);
+		}
+		CT out[VEC][KS * KS];
+#pragma unroll
+		for (int v = 0; v < VEC; v++)
+			winograd::transform_2d<M, CT>(in[v], out[v]);
+#pragma unroll
+		for (int i = 0; i < KS * KS; i++)
+		{
+			const size_t index = (static_cast<size_t>(k) * KS * KS + i) * filtersIn + c0;
+			Vec<T, VEC> result;
+			if (beta != static_cast<CT>(0))
+			{
+				const Vec<T, VEC> old = load_vec<T, VEC>(update + index);
+#pragma unroll
+				for (int v = 0; v < VEC; v++)
+					result.v[v] = from_compute<T>(alpha * out[v][i] + beta * to_compute(old.v[v]));
+			}
+			else
+			{
+#pragma unroll
+				for (int v = 0; v < VEC; v++)
+					result.v[v] = from_compute<T>(alpha * out[v][i]);
+			}
+			store_vec<T, VEC>(update + index, result);
+		}
+	}
+
+	/* ------------------------------------------------------------------------------------------------------ */
+
+	inline unsigned int blocks_for(long long threads)
+	{
+		return static_cast<unsigned int>((threads + kThreads - 1) / kThreads);
+	}
+	inline bool aligned_to(const void *ptr, size_t bytes)
+	{
+		return (reinterpret_cast<uintptr_t>(ptr) % bytes) == 0;
+	}
+	/* widest vector (in elements) that divides the channel count and matches the alignment of every pointer */
+	template<typename T, typename MT>
+	int pick_vec(int channels, int maxVec, std::initializer_list<const void*> tensorPtrs, std::initializer_list<const void*> matrixPtrs)
+	{
+		for (int vec = maxVec; vec > 1; vec /= 2)
+		{
+			bool ok = (channels % vec == 0);
+			for (const void *p : tensorPtrs)
+				ok = ok and (p == nullptr or aligned_to(p, sizeof(T) * vec));
+			for (const void *p : matrixPtrs)
+				ok = ok and (p == nullptr or aligned_to(p, sizeof(MT) * vec));
+			if (ok)
+				return vec;
+		}
+		return 1;
+	}
+
+	bool tile_config_supported(const TensorObject &wDesc, int transformSize)
+	{
+		if (wDesc.nb_dims != 4)
+			return false;
+		if (is_conv(3, wDesc))
+			return transformSize == 2 or transformSize == 4;
+		if (is_conv(5, wDesc))
+			return transformSize == 2;
+		return false;
+	}
+
+	/* Calls f(TS, KS) with the sizes as compile-time constants. */
+#define DISPATCH_TILE(kernelSize, transformSize, ...) \
+	if ((kernelSize) == 3 and (transformSize) == 2) { constexpr int TS = 2, KS = 3; __VA_ARGS__ } \
+	else if ((kernelSize) == 3 and (transformSize) == 4) { constexpr int TS = 4, KS = 3; __VA_ARGS__ } \
+	else if ((kernelSize) == 5 and (transformSize) == 2) { constexpr int TS = 2, KS = 5; __VA_ARGS__ } \
+	else return AVOCADO_STATUS_NOT_SUPPORTED;
+
+#define DISPATCH_VEC2(vec, ...) \
+	if ((vec) == 2) { constexpr int VEC = 2; __VA_ARGS__ } else { constexpr int VEC = 1; __VA_ARGS__ }
+
+	template<typename T, typename MT>
+	avStatus_t launch_weight_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const void *wPtr,
+			const TensorObject &matricesDesc, void *matricesPtr, int transformSize)
+	{
+		const int K = wDesc.dims[0], ks = wDesc.dims[1], C = wDesc.dims[3];
+		const int tile = transformSize + ks - 1;
+		if (matricesDesc.nb_dims != 3 or matricesDesc.dims[0] != tile * tile or matricesDesc.dims[1] != K or matricesDesc.dims[2] != C)
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (K == 0 or C == 0)
+			return AVOCADO_STATUS_SUCCESS;
+		const bool invert = (config.mode == AVOCADO_CROSS_CORRELATION_MODE);
+		const int vec = pick_vec<T, MT>(C, sizeof(T) == 8 ? 1 : 2, { wPtr }, { matricesPtr });
+		const unsigned int grid = blocks_for(static_cast<long long>(K) * (C / vec));
+		DISPATCH_TILE(ks, transformSize,
+				DISPATCH_VEC2(vec, kernel_weight_transform<TS, KS, T, MT, VEC> <<<grid, kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(wPtr), K, C, invert);))
+		return checkForErrors();
+	}
+
+	ConvGeometry make_geometry(const TensorObject &desc, int transformSize, const ConvolutionObject &config)
+	{
+		ConvGeometry geo;
+		geo.batch = desc.dims[0];
+		geo.height = desc.dims[1];
+		geo.width = desc.dims[2];
+		geo.channels = desc.dims[3];
+		geo.tiles_h = (geo.height + transformSize - 1) / transformSize;
+		geo.tiles_w = (geo.width + transformSize - 1) / transformSize;
+		geo.pad_h = config.padding[0];
+		geo.pad_w = config.padding[1];
+		return geo;
+	}
+	bool matrices_match(const TensorObject &matricesDesc, int tile, const ConvGeometry &geo)
+	{
+		return matricesDesc.nb_dims == 3 and matricesDesc.dims[0] == tile * tile and matricesDesc.dims[1] == geo.nb_tiles()
+				and matricesDesc.dims[2] == geo.channels;
+	}
+
+	template<typename T, typename MT>
+	avStatus_t launch_input_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const TensorObject &xDesc,
+			const void *xPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize)
+	{
+		using CT = typename ComputeType<T>::type;
+		if (xDesc.nb_dims != 4)
+			return AVOCADO_STATUS_BAD_PARAM;
+		const int ks = wDesc.dims[1];
+		const ConvGeometry geo = make_geometry(xDesc, transformSize, config);
+		if (not matrices_match(matricesDesc, transformSize + ks - 1, geo))
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (geo.nb_tiles() == 0 or geo.channels == 0)
+			return AVOCADO_STATUS_SUCCESS;
+		const CT padding_value = static_cast<CT>(to_compute(config.getPaddingValue<T>()));
+		const int vec = pick_vec<T, MT>(geo.channels, sizeof(T) == 8 ? 1 : 2, { xPtr }, { matricesPtr });
+		const unsigned int grid = blocks_for(geo.nb_tiles() * (geo.channels / vec));
+		DISPATCH_TILE(ks, transformSize,
+				DISPATCH_VEC2(vec, kernel_input_transform<TS, KS, T, MT, VEC> <<<grid, kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(xPtr), geo, padding_value);))
+		return checkForErrors();
+	}
+
+	template<typename T, typename MT>
+	avStatus_t launch_gradient_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const TensorObject &dyDesc,
+			const void *dyPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize)
+	{
+		if (dyDesc.nb_dims != 4)
+			return AVOCADO_STATUS_BAD_PARAM;
+		const int ks = wDesc.dims[1];
+		const ConvGeometry geo = make_geometry(dyDesc, transformSize, config);
+		if (not matrices_match(matricesDesc, transformSize + ks - 1, geo))
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (geo.nb_tiles() == 0 or geo.channels == 0)
+			return AVOCADO_STATUS_SUCCESS;
+		const int vec = pick_vec<T, MT>(geo.channels, sizeof(T) == 8 ? 1 : 2, { dyPtr }, { matricesPtr });
+		const unsigned int grid = blocks_for(geo.nb_tiles() * (geo.channels / vec));
+		DISPATCH_TILE(ks, transformSize,
+				DISPATCH_VEC2(vec, kernel_gradient_transform<TS, KS, T, MT, VEC> <<<grid, kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(dyPtr), geo);))
+		return checkForErrors();
+	}
+
+	template<typename T, typename MT, typename BT>
+	avStatus_t launch_output_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const void *alpha1,
+			const TensorObject &matricesDesc, const void *matricesPtr, const TensorObject &yDesc, void *yPtr, const void *bPtr, const void *alpha2,
+			const void *zPtr, const void *beta, avActivationType_t activation, int transformSize)
+	{
+		using CT = typename ComputeType<T>::type;
+		if (yDesc.nb_dims != 4)
+			return AVOCADO_STATUS_BAD_PARAM;
+		const int ks = wDesc.dims[1];
+		const ConvGeometry geo = make_geometry(yDesc, transformSize, config);
+		if (not matrices_match(matricesDesc, transformSize + ks - 1, geo))
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (geo.nb_tiles() == 0 or geo.channels == 0)
+			return AVOCADO_STATUS_SUCCESS;
+		const CT a1 = getAlphaValue<CT>(alpha1);
+		const CT a2 = getAlphaValue<CT>(alpha2);
+		const CT b = getBetaValue<CT>(beta);
+		const int vec = pick_vec<T, MT>(geo.channels, sizeof(T) == 8 ? 1 : 2, { yPtr, zPtr }, { matricesPtr });
+		const unsigned int grid = blocks_for(geo.nb_tiles() * (geo.channels / vec));
+		DISPATCH_TILE(ks, transformSize,
+				DISPATCH_VEC2(vec, kernel_output_transform<TS, KS, T, MT, BT, VEC> <<<grid, kThreads, 0, ctx.getStream()>>>(reinterpret_cast<const MT*>(matricesPtr), reinterpret_cast<T*>(yPtr), geo, reinterpret_cast<const BT*>(bPtr), reinterpret_cast<const T*>(zPtr), a1, a2, b, activation);))
+		return checkForErrors();
+	}
+
+	template<typename T>
+	avStatus_t launch_update_transform(ContextObject &ctx, const void *alpha, const TensorObject &matricesDesc, const void *matricesPtr, const void *beta,
+			const TensorObject &dwDesc, void *dwPtr, int transformSize)
+	{
+		using CT = typename ComputeType<T>::type;
+		const int K = dwDesc.dims[0], ks = dwDesc.dims[1], C = dwDesc.dims[3];
+		const int tile = transformSize + ks - 1;
+		if (matricesDesc.nb_dims != 3 or matricesDesc.dims[0] != tile * tile or matricesDesc.dims[1] != K or matricesDesc.dims[2] != C)
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (K == 0 or C == 0)
+			return AVOCADO_STATUS_SUCCESS;
+		const CT a = getAlphaValue<CT>(alpha);
+		const CT b = getBetaValue<CT>(beta);
+		const int vec = pick_vec<T, T>(C, sizeof(T) == 8 ? 1 : 2, { dwPtr }, { matricesPtr });
+		const unsigned int grid = blocks_for(static_cast<long long>(K) * (C / vec));
+		DISPATCH_TILE(ks, transformSize,
+				DISPATCH_VEC2(vec, kernel_update_transform<TS, KS, T, VEC> <<<grid, kThreads, 0, ctx.getStream()>>>(reinterpret_cast<const T*>(matricesPtr), reinterpret_cast<T*>(dwPtr), K, C, a, b);))
+		return checkForErrors();
+	}
+
+	/* which (tensor dtype, matrices dtype) pairs exist: equal types, or 16-bit tensors with float32 matrices */
+	enum class Pairing
+	{
+		F16_F16, F16_F32, BF16_BF16, BF16_F32, F32_F32, F64_F64, Unsupported
+	};
+	Pairing classify(avDataType_t tensorType, avDataType_t matrixType)
+	{
+		switch (tensorType)
+		{
+			case AVOCADO_DTYPE_FLOAT16:
+				return matrixType == AVOCADO_DTYPE_FLOAT16 ? Pairing::F16_F16 : matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::F16_F32 : Pairing::Unsupported;
+			case AVOCADO_DTYPE_BFLOAT16:
+				return matrixType == AVOCADO_DTYPE_BFLOAT16 ? Pairing::BF16_BF16 : matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::BF16_F32 : Pairing::Unsupported;
+			case AVOCADO_DTYPE_FLOAT32:
+				return matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::F32_F32 : Pairing::Unsupported;
+			case AVOCADO_DTYPE_FLOAT64:
+				return matrixType == AVOCADO_DTYPE_FLOAT64 ? Pairing::F64_F64 : Pairing::Unsupported;
+			default:
+				return Pairing::Unsupported;
+		}
+	}
+}
+
+namespace avocado
+{
+	namespace backend
+	{
+		avStatus_t cudaWinogradWeightTransform(avContextDescriptor_t context, const avConvolutionDescriptor_t config, int transformSize,
+				const avTensorDescriptor_t wDesc, const avMemoryDescriptor_t wMem, const avTensorDescriptor_t matricesDesc, avMemoryDescriptor_t matricesMem)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				const ConvolutionObject &conv = getConvolution(config);
+				const TensorObject &w = getTensor(wDesc);
+				const TensorObject &m = getTensor(matricesDesc);
+				const void *wPtr = getPointer(wMem);
+				void *mPtr = getPointer(matricesMem);
+				if (not tile_config_supported(w, transformSize))
+					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+				if (wPtr == nullptr or mPtr == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM;
+				ctx.setDevice();
+				switch (classify(w.dtype, m.dtype))
+				{
+					case Pairing::F16_F16:
+						return launch_weight_transform<half, half>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+					case Pairing::F16_F32:
+						return launch_weight_transform<half, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+					case Pairing::BF16_BF16:
+						return launch_weight_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+					case Pairing::BF16_F32:
+						return launch_weight_transform<__nv_bfloat16, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+					case Pairing::F32_F32:
+						return launch_weight_transform<float, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+					case Pairing::F64_F64:
+						return launch_weight_transform<double, double>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+					default:
+						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				}
+			AVOCADO_API_END
+		}
+
+		avStatus_t cudaWinogradInputTransform(avContextDescriptor_t context, const avConvolutionDescriptor_t config, int transformSize,
+				const avTensorDescriptor_t wDesc, const avTensorDescriptor_t xDesc, const avMemoryDescriptor_t xMem, const avTensorDescriptor_t matricesDesc,
+				avMemoryDescriptor_t matricesMem)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				const ConvolutionObject &conv = getConvolution(config);
+				const TensorObject &w = getTensor(wDesc);
+				const TensorObject &x = getTensor(xDesc);
+				const TensorObject &m = getTensor(matricesDesc);
+				const void *xPtr = getPointer(xMem);
+				void *mPtr = getPointer(matricesMem);
+				if (not tile_config_supported(w, transformSize))
+					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+				if (xPtr == nullptr or mPtr == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM;
+				ctx.setDevice();
+				/* the reference switches on the dtype of w (src/winograd_nonfused.cu:914); x must agree with it */
+				if (x.dtype != w.dtype)
+					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				switch (classify(w.dtype, m.dtype))
+				{
+					case Pairing::F16_F16:
+						return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+					case Pairing::F16_F32:
+						return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+					case Pairing::BF16_BF16:
+						return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+					case Pairing::BF16_F32:
+						return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+					case Pairing::F32_F32:
+						return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+					case Pairing::F64_F64:
+						return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+					default:
+						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				}
+			AVOCADO_API_END
+		}
+
+		avStatus_t cudaWinogradOutputTransform(avContextDescriptor_t context, const avConvolutionDescriptor_t config, int transformSize,
+				const avTensorDescriptor_t wDesc, const void *alpha1, const avTensorDescriptor_t matricesDesc, const avMemoryDescriptor_t matricesMem,
+				const avTensorDescriptor_t yDesc, avMemoryDescriptor_t yMem, const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem,
+				const void *alpha2, const avTensorDescriptor_t zDesc, const avMemoryDescriptor_t zMem, const void *beta, avActivationType_t activation)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				const ConvolutionObject &conv = getConvolution(config);
+				const TensorObject &w = getTensor(wDesc);
+				const TensorObject &m = getTensor(matricesDesc);
+				const TensorObject &y = getTensor(yDesc);
+				const void *mPtr = getPointer(matricesMem);
+				void *yPtr = getPointer(yMem);
+				const void *bPtr = getPointer(bMem);
+				const void *zPtr = getPointer(zMem);
+				(void) bDesc;
+				(void) zDesc;
+				if (not tile_config_supported(w, transformSize))
+					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+				if (yPtr == nullptr or mPtr == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM;
+				if (y.dtype != w.dtype)
+					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				ctx.setDevice();
+				switch (classify(w.dtype, m.dtype))
+				{
+					case Pairing::F16_F16:
+						return launch_output_transform<half, half, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+								transformSize);
+					case Pairing::F16_F32:
+						return launch_output_transform<half, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+								transformSize);
+					case Pairing::BF16_BF16:
+						return launch_output_transform<__nv_bfloat16, __nv_bfloat16, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta,
+								activation, transformSize);
+					case Pairing::BF16_F32:
+						return launch_output_transform<__nv_bfloat16, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+								transformSize);
+					case Pairing::F32_F32:
+						return launch_output_transform<float, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+								transformSize);
+					case Pairing::F64_F64:
+						return launch_output_transform<double, double, double>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+								transformSize);
+					default:
+						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				}
+			AVOCADO_API_END
+		}
+
+		avStatus_t cudaWinogradGradientTransform(avContextDescriptor_t context, const avConvolutionDescriptor_t config, int transformSize,
+				const avTensorDescriptor_t wDesc, const avTensorDescriptor_t dyDesc, const avMemoryDescriptor_t dyMem, const avTensorDescriptor_t matricesDesc,
+				avMemoryDescriptor_t matricesMem)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				const ConvolutionObject &conv = getConvolution(config);
+				const TensorObject &w = getTensor(wDesc);
+				const TensorObject &dy = getTensor(dyDesc);
+				const TensorObject &m = getTensor(matricesDesc);
+				const void *dyPtr = getPointer(dyMem);
+				void *mPtr = getPointer(matricesMem);
+				if (not tile_config_supported(w, transformSize))
+					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+				if (dyPtr == nullptr or mPtr == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM;
+				if (dy.dtype != w.dtype or m.dtype != w.dtype)
+					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				ctx.setDevice();
+				/* float32 and float64 only, as in the reference (src/winograd_nonfused.cu:971-979) */
+				switch (w.dtype)
+				{
+					case AVOCADO_DTYPE_FLOAT32:
+						return launch_gradient_transform<float, float>(ctx, conv, w, dy, dyPtr, m, mPtr, transformSize);
+					case AVOCADO_DTYPE_FLOAT64:
+						return launch_gradient_transform<double, double>(ctx, conv, w, dy, dyPtr, m, mPtr, transformSize);
+					default:
+						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				}
+			AVOCADO_API_END
+		}
+
+		avStatus_t cudaWinogradUpdateTransform(avContextDescriptor_t context, const avConvolutionDescriptor_t config, int transformSize, const void *alpha,
+				const avTensorDescriptor_t matricesDesc, const avMemoryDescriptor_t matricesMem, const void *beta, const avTensorDescriptor_t dwDesc,
+				avMemoryDescriptor_t dwMem)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				(void) getConvolution(config);
+				const TensorObject &m = getTensor(matricesDesc);
+				const TensorObject &dw = getTensor(dwDesc);
+				const void *mPtr = getPointer(matricesMem);
+				void *dwPtr = getPointer(dwMem);
+				if (not tile_config_supported(dw, transformSize))
+					return (dw.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+				if (dwPtr == nullptr or mPtr == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM;
+				if (m.dtype != dw.dtype)
+					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				ctx.setDevice();
+				switch (dw.dtype)
+				{
+					case AVOCADO_DTYPE_FLOAT32:
+						return launch_update_transform<float>(ctx, alpha, m, mPtr, beta, dw, dwPtr, transformSize);
+					case AVOCADO_DTYPE_FLOAT64:
+						return launch_update_transform<double>(ctx, alpha, m, mPtr, beta, dw, dwPtr, transformSize);
+					default:
+						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				}
+			AVOCADO_API_END
+		}
+	} /* namespace backend */
+} /* namespace avocado */

@@ -1,0 +1,218 @@
+"""numpy front end of the CPU oracle (oracle/conv_oracle.c).  TEST INFRASTRUCTURE ONLY.
+
+Only tests/, __graft_entry__.smoke() and the cpu_baseline / reference arm of bench.py may import this module;
+the product (cudabackend_b200) never does.  Every function takes and returns numpy arrays in the layouts of the
+reference: activations NHWC, filters [K, kh, kw, C], transform-domain matrices [tile*tile, nbTiles, channels].
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+ACTIVATIONS = {"linear": 0, "sigmoid": 1, "tanh": 2, "relu": 3, "selu": 4, "elu": 5, "exponential": 6, "softplus": 7, "softsign": 8}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = _build.LIB
+        if os.path.exists(os.path.join(_build.HERE, "conv_oracle.c")) and _have_gcc():
+            path = _build.build()
+        _lib = ctypes.CDLL(path)
+        _lib.oracle_max_threads.restype = ctypes.c_int
+    return _lib
+
+
+def _have_gcc():
+    import shutil
+    return shutil.which("gcc") is not None
+
+
+def max_threads():
+    return int(lib().oracle_max_threads())
+
+
+def _p(a, ctype):
+    if a is None:
+        return ctypes.POINTER(ctype)()
+    return a.ctypes.data_as(ctypes.POINTER(ctype))
+
+
+def _f64(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float64)
+
+
+def _act(activation):
+    return ACTIVATIONS[activation] if isinstance(activation, str) else int(activation)
+
+
+def conv2d_forward(x, w, bias=None, z=None, y=None, padding=(-1, -1), mode=0, padding_value=0.0, alpha1=1.0, alpha2=1.0, beta=0.0,
+                   activation="linear", out_hw=None):
+    """float64 direct convolution with the reference's epilogue; returns y[N,Ho,Wo,K]."""
+    x, w, bias, z = _f64(x), _f64(w), _f64(bias), _f64(z)
+    N, H, W, C = x.shape
+    K, kh, kw, _ = w.shape
+    Ho, Wo = out_hw if out_hw is not None else (H, W)
+    out = np.zeros((N, Ho, Wo, K), dtype=np.float64) if y is None else np.array(y, dtype=np.float64, order="C")
+    d = ctypes.c_double
+    lib().oracle_conv2d_forward_f64(_p(x, d), _p(w, d), _p(bias, d), _p(z, d), _p(out, d), N, H, W, C, Ho, Wo, K, kh, kw, int(padding[0]),
+                                    int(padding[1]), int(mode), d(padding_value), d(alpha1), d(alpha2), d(beta), _act(activation))
+    return out
+
+
+def conv2d_backward_data(dy, w, x_hw, padding=(-1, -1)):
+    dy, w = _f64(dy), _f64(w)
+    N, Ho, Wo, K = dy.shape
+    _, kh, kw, C = w.shape
+    H, W = x_hw
+    dx = np.zeros((N, H, W, C), dtype=np.float64)
+    d = ctypes.c_double
+    lib().oracle_conv2d_backward_data_f64(_p(dy, d), _p(w, d), _p(dx, d), N, H, W, C, Ho, Wo, K, kh, kw, int(padding[0]), int(padding[1]))
+    return dx
+
+
+def conv2d_backward_weights(x, dy, kernel=(3, 3), padding=(-1, -1)):
+    x, dy = _f64(x), _f64(dy)
+    N, H, W, C = x.shape
+    _, Ho, Wo, K = dy.shape
+    kh, kw = kernel
+    dw = np.zeros((K, kh, kw, C), dtype=np.float64)
+    d = ctypes.c_double
+    lib().oracle_conv2d_backward_weights_f64(_p(x, d), _p(dy, d), _p(dw, d), N, H, W, C, Ho, Wo, K, kh, kw, int(padding[0]), int(padding[1]))
+    return dw
+
+
+def conv2d_forward_f32_naive(x, w, bias=None, padding=(-1, -1), relu=False):
+    """The float32 naive convolution used as the timed CPU baseline (not the correctness oracle)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    N, H, W, C = x.shape
+    K, kh, kw, _ = w.shape
+    y = np.empty((N, H, W, K), dtype=np.float32)
+    f = ctypes.c_float
+    lib().oracle_conv2d_forward_f32_naive(_p(x, f), _p(w, f), _p(bias, f), _p(y, f), N, H, W, C, K, kh, kw, int(padding[0]), int(padding[1]), int(relu))
+    return y
+
+
+def conv2d_forward_int8(x, w, bias=None, scale=None, z=None, padding=(-1, -1), alpha1=1.0, alpha2=1.0, activation="linear", int32_output=False):
+    """Exact int8 convolution; returns int8 (requantised) or int32 (raw accumulator + bias)."""
+    x = np.ascontiguousarray(x, dtype=np.int8)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.int32)
+    scale = None if scale is None else np.ascontiguousarray(scale, dtype=np.float32)
+    z = None if z is None else np.ascontiguousarray(z, dtype=np.int8)
+    N, H, W, C = x.shape
+    K, kh, kw, _ = w.shape
+    y8 = None if int32_output else np.empty((N, H, W, K), dtype=np.int8)
+    y32 = np.empty((N, H, W, K), dtype=np.int32) if int32_output else None
+    lib().oracle_conv2d_forward_int8(_p(x, ctypes.c_int8), _p(w, ctypes.c_int8), _p(bias, ctypes.c_int32), _p(scale, ctypes.c_float),
+                                     _p(z, ctypes.c_int8), _p(y8, ctypes.c_int8), _p(y32, ctypes.c_int32), N, H, W, C, K, kh, kw, int(padding[0]),
+                                     int(padding[1]), ctypes.c_float(alpha1), ctypes.c_float(alpha2), _act(activation))
+    return y32 if int32_output else y8
+
+
+TABLE_KINDS = {"weight": 0, "input": 1, "output": 2, "gradient": 3, "update": 4}
+
+
+def winograd_table(transform_size, kernel_size, kind):
+    buf = np.zeros(64, dtype=np.float64)
+    rows, cols = ctypes.c_int(0), ctypes.c_int(0)
+    n = lib().oracle_winograd_table(transform_size, kernel_size, TABLE_KINDS[kind], _p(buf, ctypes.c_double), ctypes.byref(rows), ctypes.byref(cols))
+    if n == 0:
+        raise ValueError("unsupported Winograd configuration")
+    return buf[:n].reshape(rows.value, cols.value).copy()
+
+
+def nb_tiles(N, H, W, transform_size):
+    return N * ((H + transform_size - 1) // transform_size) * ((W + transform_size - 1) // transform_size)
+
+
+def winograd_weight_transform(w, transform_size, invert=False):
+    w = _f64(w)
+    K, ks, _, C = w.shape
+    tile = transform_size + ks - 1
+    out = np.zeros((tile * tile, K, C), dtype=np.float64)
+    d = ctypes.c_double
+    if lib().oracle_winograd_weight_transform_f64(_p(w, d), _p(out, d), K, C, transform_size, ks, int(invert)) != 0:
+        raise ValueError("unsupported Winograd configuration")
+    return out
+
+
+def winograd_input_transform(x, transform_size, kernel_size, padding=(-1, -1), padding_value=0.0):
+    x = _f64(x)
+    N, H, W, C = x.shape
+    tile = transform_size + kernel_size - 1
+    out = np.zeros((tile * tile, nb_tiles(N, H, W, transform_size), C), dtype=np.float64)
+    d = ctypes.c_double
+    if lib().oracle_winograd_input_transform_f64(_p(x, d), _p(out, d), N, H, W, C, transform_size, kernel_size, int(padding[0]), int(padding[1]),
+                                                 d(padding_value)) != 0:
+        raise ValueError("unsupported Winograd configuration")
+    return out
+
+
+def winograd_output_transform(matrices, shape, transform_size, kernel_size, bias=None, z=None, y=None, alpha1=1.0, alpha2=1.0, beta=0.0,
+                              activation="linear"):
+    matrices, bias, z = _f64(matrices), _f64(bias), _f64(z)
+    N, H, W, K = shape
+    out = np.zeros(shape, dtype=np.float64) if y is None else np.array(y, dtype=np.float64, order="C")
+    d = ctypes.c_double
+    if lib().oracle_winograd_output_transform_f64(_p(matrices, d), _p(out, d), _p(bias, d), _p(z, d), N, H, W, K, transform_size, kernel_size,
+                                                  d(alpha1), d(alpha2), d(beta), _act(activation)) != 0:
+        raise ValueError("unsupported Winograd configuration")
+    return out
+
+
+def winograd_gradient_transform(dy, transform_size, kernel_size):
+    dy = _f64(dy)
+    N, H, W, K = dy.shape
+    tile = transform_size + kernel_size - 1
+    out = np.zeros((tile * tile, nb_tiles(N, H, W, transform_size), K), dtype=np.float64)
+    d = ctypes.c_double
+    if lib().oracle_winograd_gradient_transform_f64(_p(dy, d), _p(out, d), N, H, W, K, transform_size, kernel_size) != 0:
+        raise ValueError("unsupported Winograd configuration")
+    return out
+
+
+def winograd_update_transform(matrices, transform_size, kernel_size, dw=None, alpha=1.0, beta=0.0):
+    matrices = _f64(matrices)
+    _, K, C = matrices.shape
+    out = np.zeros((K, kernel_size, kernel_size, C), dtype=np.float64) if dw is None else np.array(dw, dtype=np.float64, order="C")
+    d = ctypes.c_double
+    if lib().oracle_winograd_update_transform_f64(_p(matrices, d), _p(out, d), K, C, transform_size, kernel_size, d(alpha), d(beta)) != 0:
+        raise ValueError("unsupported Winograd configuration")
+    return out
+
+
+def gemm_batched(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
+    """C[i] = alpha * op(A[i]) * op(B[i]) + beta * C[i] in float64 (row-major 3-D arrays)."""
+    a, b = _f64(a), _f64(b)
+    opa = np.swapaxes(a, 1, 2) if trans_a else a
+    opb = np.swapaxes(b, 1, 2) if trans_b else b
+    out = alpha * np.matmul(opa, opb)
+    if c is not None and beta != 0.0:
+        out = out + beta * np.asarray(c, dtype=np.float64)
+    return out
+
+
+def error_metrics(result, reference):
+    """The three error figures quoted for floating-point parity.
+
+    elem: max |e| / max(|ref|, rms(ref))  (headline; plain relative error is meaningless where ref crosses zero)
+    norm: max |e| / max |ref|
+    rms:  rms(e) / rms(ref)
+    """
+    result = np.asarray(result, dtype=np.float64)
+    reference = np.asarray(reference, dtype=np.float64)
+    err = np.abs(result - reference)
+    rms_ref = float(np.sqrt(np.mean(reference * reference)))
+    if rms_ref == 0.0:
+        rms_ref = 1.0
+    elem = float(np.max(err / np.maximum(np.abs(reference), rms_ref))) if err.size else 0.0
+    norm = float(np.max(err) / max(float(np.max(np.abs(reference))), 1e-300)) if err.size else 0.0
+    rms = float(np.sqrt(np.mean(err * err)) / rms_ref) if err.size else 0.0
+    return {"elem": elem, "norm": norm, "rms": rms}

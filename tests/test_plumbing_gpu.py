@@ -1,0 +1,74 @@
+"""GPU tests of the descriptor plumbing (reference src/descriptors.cu:48-253)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from cudabackend_b200 import api
+
+pytestmark = pytest.mark.gpu
+
+
+def test_memory_copy_round_trip_and_views(ctx):
+    data = np.arange(4096, dtype=np.float32)
+    mem = api.Memory(data.nbytes)
+    mem.from_host(ctx, data)
+    back = np.empty_like(data)
+    mem.to_host(ctx, back)
+    ctx.synchronize()
+    assert np.array_equal(back, data)
+    view = mem.view(1024, 2048)
+    part = np.empty(256, dtype=np.float32)
+    view.to_host(ctx, part)
+    ctx.synchronize()
+    assert np.array_equal(part, data[512:768])
+    # a view of a view is refused, like a negative offset
+    h = ctypes.c_int64(-1)
+    assert api.call_status("cudaCreateMemoryView", ctypes.byref(h), view.handle, 16, 0) == api.STATUS["BAD_PARAM"]
+    assert api.call_status("cudaCreateMemoryView", ctypes.byref(h), mem.handle, 16, -4) == api.STATUS["BAD_PARAM"]
+    assert api.call_status("cudaCreateMemoryView", ctypes.byref(h), mem.handle, 16, data.nbytes) == api.STATUS["BAD_PARAM"]
+
+
+@pytest.mark.parametrize("pattern_size", [1, 2, 4, 8, 16])
+def test_set_memory_patterns(ctx, pattern_size):
+    mem = api.Memory(4096)
+    mem.zero(ctx)
+    pattern = bytes(range(1, pattern_size + 1))
+    buf = ctypes.create_string_buffer(pattern, pattern_size)
+    api.call("cudaSetMemory", ctx.handle, mem.handle, 1024, 2048, ctypes.cast(buf, ctypes.c_void_p), pattern_size)
+    out = np.empty(4096, dtype=np.uint8)
+    mem.to_host(ctx, out)
+    ctx.synchronize()
+    assert not out[:1024].any() and not out[3072:].any()
+    assert out[1024:3072].tobytes() == pattern * (2048 // pattern_size)
+    assert api.call_status("cudaSetMemory", ctx.handle, mem.handle, 0, 100, ctypes.cast(buf, ctypes.c_void_p), 3) == api.STATUS["BAD_PARAM"]
+
+
+def test_device_copy_and_default_context(library, device_count):
+    if device_count == 0:
+        pytest.skip("no CUDA device visible")
+    ctx = api.Context.default(0)
+    a = api.Memory(1024)
+    b = api.Memory(1024)
+    data = np.random.default_rng(0).integers(0, 255, 1024, dtype=np.uint8)
+    a.from_host(ctx, data)
+    api.call("cudaCopyMemory", ctx.handle, b.handle, 0, a.handle, 0, 1024)
+    out = np.empty_like(data)
+    b.to_host(ctx, out)  # synchronous on a default context
+    assert np.array_equal(out, data)
+    assert api.call_status("cudaDestroyContextDescriptor", ctx.handle) == api.STATUS["BAD_PARAM"]
+    possible = ctypes.c_bool(False)
+    api.call("cudaIsCopyPossible", 0, 0, ctypes.byref(possible))
+    assert possible.value
+
+
+def test_context_ready_and_properties(ctx):
+    ctx.synchronize()
+    assert ctx.is_ready()
+    name = ctypes.create_string_buffer(256)
+    api.call("cudaGetDeviceProperty", 0, 0, ctypes.cast(name, ctypes.c_void_p))
+    assert len(name.value) > 0
+    sms = (ctypes.c_int32 * 64)()
+    api.call("cudaGetDeviceProperty", 0, 1, ctypes.cast(sms, ctypes.c_void_p))
+    assert sms[0] > 0
+    assert ctx.last_device_status() == 0
