@@ -314,39 +314,37 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             dist.barrier()
         sync_all()
 
+    use_graph = (not args.no_graph) and grad_views is None
+
     # ---- device-timed region ------------------------------------------------------------------------------
-    # every buffer set is driven through ONE context (one stream) here, so steps run back to back on the device
+    # every buffer set is driven through ONE context (one stream) here, so steps run back to back on the device;
+    # a step is replayed from a captured graph (one launch per step instead of one per kernel)
     shared_ctx = sets[0].ctx
     own_ctx = [ws.ctx for ws in sets]
     for ws in sets:
         ws.ctx = shared_ctx
         ws.p.ctx = shared_ctx
     s0 = streams[0]
+    graphs = [shared_ctx.capture(ws.step) for ws in sets] if use_graph else None
+
+    def timed_step(i):
+        if graphs is not None:
+            graphs[i % rotation].launch()
+        else:
+            full_step(i)
+
     for i in range(args.warmup):
-        full_step(i)
+        timed_step(i)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    stage_names = [name for name, _ in sets[0].stages()]
-    stage_events = []
     first = torch.cuda.Event(enable_timing=True)
     last = torch.cuda.Event(enable_timing=True)
     t_wall0 = time.perf_counter()
     first.record(s0)
     for i in range(args.steps):
-        ws = sets[i % rotation]
-        marks = [torch.cuda.Event(enable_timing=True)]
-        marks[0].record(s0)
-        for name, fn in ws.stages():
-            fn()
-            e = torch.cuda.Event(enable_timing=True)
-            e.record(s0)
-            marks.append(e)
-        if grad_views is not None:
-            with torch.cuda.stream(s0):
-                dist.all_reduce(grad_views[i % rotation])
-        stage_events.append(marks)
+        timed_step(i)
     last.record(s0)
     sync_all()
     elapsed_ms = first.elapsed_time(last)
@@ -356,35 +354,67 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
-    stage_ms = {name: statistics.mean(m[j].elapsed_time(m[j + 1]) for m in stage_events) for j, name in enumerate(stage_names)}
 
-    status = sum(ws.ctx.last_device_status() for ws in sets)
+    # ---- per-kernel durations: each stage launched back to back over the rotating buffer sets, CUDA events around ---
+    stage_names = [name for name, _ in sets[0].stages()]
+    stage_ms = {}
+    stage_reps = max(20, min(args.steps, 200))
+    for j, name in enumerate(stage_names):
+        fns = [ws.stages()[j][1] for ws in sets]
+        for i in range(rotation):
+            fns[i]()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        shared_ctx.synchronize()
+        e0.record(s0)
+        for i in range(stage_reps):
+            fns[i % rotation]()
+        e1.record(s0)
+        sync_all()
+        stage_ms[name] = e0.elapsed_time(e1) / stage_reps
+
+    status = sum(ctx.last_device_status() for ctx in own_ctx)
     if status != 0:
         raise RuntimeError("a tensor-core kernel reported a bounded wait that ran out (status %d)" % status)
 
-    # ---- end-to-end region: pinned host buffers, copies inside ------------------------------------------------
+    # ---- end-to-end region: pinned host buffers, copies inside; one stream per buffer set so copies overlap kernels --
     for ws, ctx in zip(sets, own_ctx):
         ws.ctx = ctx
         ws.p.ctx = ctx
         ws.pin_host_buffers(data)
-    for i in range(min(args.warmup, rotation)):
-        sets[i % rotation].step_e2e()
+    e2e_graphs = [ws.ctx.capture(ws.step_e2e) for ws in sets] if use_graph else None
+
+    def e2e_step(i):
+        if e2e_graphs is not None:
+            e2e_graphs[i % rotation].launch()
+        else:
+            sets[i % rotation].step_e2e()
+            if grad_views is not None:
+                with torch.cuda.stream(streams[i % rotation]):
+                    dist.all_reduce(grad_views[i % rotation])
+
+    for i in range(min(args.warmup, 2 * rotation)):
+        e2e_step(i)
     barrier()
+    e2e_steps = max(rotation, min(args.steps, 400))
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        ws = sets[i % rotation]
-        ws.step_e2e()
-        if grad_views is not None:
-            with torch.cuda.stream(streams[i % rotation]):
-                dist.all_reduce(grad_views[i % rotation])
+    for i in range(e2e_steps):
+        e2e_step(i)
     sync_all()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = (time.perf_counter() - t0) * args.steps / e2e_steps
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     h2d = sets[0].host_x.nbytes
     d2h = sets[0].host_y.nbytes
+    sync_all()
+    if e2e_graphs is not None:
+        for gr in e2e_graphs:
+            gr.destroy()
+    if graphs is not None:
+        for gr in graphs:
+            gr.destroy()
     for ws in sets:
         ws.unpin()
 
@@ -409,7 +439,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             "host_wall_ms_per_step": wall_ms / args.steps,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "images_per_s": cfg["n"] * args.steps * world / e2e_s, "ms_per_step": 1e3 * e2e_s / args.steps},
-            "gpu_launches": sets[0].launches_per_step() * args.steps, "stage_ms": stage_ms, "clocks": clocks}
+            "gpu_launches": sets[0].launches_per_step() * args.steps, "launch_mode": "cuda graph, one launch per step" if use_graph else "kernel by kernel",
+            "stage_ms": stage_ms, "clocks": clocks}
 
     # roofline of the dominant kernel
     if cfg["kind"] == "winograd_nonfused":
@@ -447,13 +478,14 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
     parser.add_argument("--matrices", default=None, choices=["float16", "bfloat16", "float32"], help="dtype of the transform-domain tensors")
     parser.add_argument("--rotation", type=int, default=4, help="buffer sets rotated between steps")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    parser.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a captured graph")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -75,6 +75,10 @@ SIGNATURES = {
     "cudaGetMemoryPointer": (_INT, [_H, ctypes.POINTER(_VP)]),
     "cudaGetContextStream": (_INT, [_H, ctypes.POINTER(_VP)]),
     "cudaGetLastDeviceStatus": (_INT, [_H, ctypes.POINTER(_INT)]),
+    "cudaContextBeginCapture": (_INT, [_H]),
+    "cudaContextEndCapture": (_INT, [_H, ctypes.POINTER(_I64)]),
+    "cudaContextLaunchGraph": (_INT, [_H, _I64]),
+    "cudaDestroyCapturedGraph": (_INT, [_I64]),
 }
 
 # exported for link compatibility, return NOT_SUPPORTED
@@ -170,10 +174,48 @@ class Context:
         call("cudaGetLastDeviceStatus", self.handle, ctypes.byref(r))
         return int(r.value)
 
+    def capture(self, fn):
+        """Runs fn() once for its side effects on the stream, then records a second run of it into a graph."""
+        fn()
+        self.synchronize()
+        call("cudaContextBeginCapture", self.handle)
+        try:
+            fn()
+        finally:
+            g = _I64(0)
+            status = call_status("cudaContextEndCapture", self.handle, ctypes.byref(g))
+        check("cudaContextEndCapture", status)
+        return Graph(self, g.value)
+
     def destroy(self):
         if self._owned and self.handle != INVALID:
             call("cudaDestroyContextDescriptor", self.handle)
         self.handle = INVALID
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class Graph:
+    """A recorded sequence of API calls on one context (cudaContextBeginCapture / EndCapture), replayed by launch()."""
+
+    def __init__(self, ctx, handle):
+        self.ctx = ctx
+        self.handle = handle
+        self._launch = load().cudaContextLaunchGraph
+
+    def launch(self):
+        status = self._launch(self.ctx.handle, self.handle)
+        if status != 0:
+            raise AvocadoError("cudaContextLaunchGraph", status)
+
+    def destroy(self):
+        if self.handle:
+            call("cudaDestroyCapturedGraph", self.handle)
+        self.handle = 0
 
     def __del__(self):
         try:

@@ -845,5 +845,58 @@ namespace avocado
 				return AVOCADO_STATUS_SUCCESS;
 			AVOCADO_API_END
 		}
+
+		avStatus_t cudaContextBeginCapture(avContextDescriptor_t context)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				if (ctx.is_default)
+					return AVOCADO_STATUS_BAD_PARAM;
+				ctx.setDevice();
+				return convertStatus(cudaStreamBeginCapture(ctx.getStream(), cudaStreamCaptureModeRelaxed));
+			AVOCADO_API_END
+		}
+		avStatus_t cudaContextEndCapture(avContextDescriptor_t context, av_int64 *graph)
+		{
+			if (graph == nullptr)
+				return AVOCADO_STATUS_BAD_PARAM;
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				ctx.setDevice();
+				cudaGraph_t captured = nullptr;
+				cudaError_t status = cudaStreamEndCapture(ctx.getStream(), &captured);
+				if (status != cudaSuccess or captured == nullptr)
+				{
+					cudaGetLastError();
+					return AVOCADO_STATUS_EXECUTION_FAILED;
+				}
+				cudaGraphExec_t executable = nullptr;
+				status = cudaGraphInstantiate(&executable, captured, 0);
+				cudaGraphDestroy(captured);
+				if (status != cudaSuccess)
+				{
+					cudaGetLastError();
+					return AVOCADO_STATUS_EXECUTION_FAILED;
+				}
+				graph[0] = static_cast<av_int64>(reinterpret_cast<intptr_t>(executable));
+				return AVOCADO_STATUS_SUCCESS;
+			AVOCADO_API_END
+		}
+		avStatus_t cudaContextLaunchGraph(avContextDescriptor_t context, av_int64 graph)
+		{
+			if (graph == 0)
+				return AVOCADO_STATUS_BAD_PARAM;
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				ctx.setDevice();
+				return convertStatus(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(static_cast<intptr_t>(graph)), ctx.getStream()));
+			AVOCADO_API_END
+		}
+		avStatus_t cudaDestroyCapturedGraph(av_int64 graph)
+		{
+			if (graph == 0)
+				return AVOCADO_STATUS_BAD_PARAM;
+			return convertStatus(cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(static_cast<intptr_t>(graph))));
+		}
 	} /* namespace backend */
 } /* namespace avocado */

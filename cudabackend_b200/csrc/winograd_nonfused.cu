@@ -19,8 +19,13 @@
 #include "objects.hpp"
 #include "device_utils.cuh"
 #include "winograd_tables.cuh"
+#include "winograd_f43.cuh"
 
 #include <cuda_runtime_api.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace
 {
@@ -410,6 +415,183 @@ namespace
 				and matricesDesc.dims[2] == geo.channels;
 	}
 
+
+	/* ------------------------------------------------------------------------------------------------------
+	 * F(4x4,3x3) fast paths (winograd_f43.cuh).  Each returns NOT_SUPPORTED when the case is outside what the
+	 * fast kernel covers; the caller then launches the generic kernel.
+	 * ------------------------------------------------------------------------------------------------------ */
+	template<typename T> struct TmaType;
+	template<> struct TmaType<half>
+	{
+			static constexpr CUtensorMapDataType value = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+	};
+	template<> struct TmaType<__nv_bfloat16>
+	{
+			static constexpr CUtensorMapDataType value = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+	};
+	template<> struct TmaType<float>
+	{
+			static constexpr CUtensorMapDataType value = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+	};
+
+	template<typename T, typename MT>
+	avStatus_t launch_f43_input(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr)
+	{
+		if (cuda_sm_version(ctx.device) != 100 or not config.paddingValueIsZero())
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		if ((geo.channels * sizeof(T)) % 16 != 0 or not aligned_to(xPtr, 16) or not aligned_to(matricesPtr, 2 * sizeof(MT)))
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		/* a strip is at most 8 tiles (one per warp) and its halo box at most 48 KB */
+		const int max_pixels = 48 * 1024 / (f43::kChannelBlock * static_cast<int>(sizeof(T)));
+		const int max_tw = std::min(8, (max_pixels / 6 - 2) / 4);
+		const int segments = (geo.tiles_w + max_tw - 1) / max_tw;
+		f43::InputGeometry g;
+		g.strip_tiles_w = (geo.tiles_w + segments - 1) / segments;
+		g.box_w = 4 * g.strip_tiles_w + 2;
+		g.strip_tiles_h = std::max(1, std::min(std::min(geo.tiles_h, 8 / g.strip_tiles_w), (max_pixels / g.box_w - 2) / 4));
+		const int box_h = 4 * g.strip_tiles_h + 2;
+		if (g.box_w > 256 or box_h > 256)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		g.batch = geo.batch;
+		g.tiles_h = geo.tiles_h;
+		g.tiles_w = geo.tiles_w;
+		g.channels = geo.channels;
+		g.pad_h = geo.pad_h;
+		g.pad_w = geo.pad_w;
+		g.row_groups = (geo.tiles_h + g.strip_tiles_h - 1) / g.strip_tiles_h;
+		g.w_segments = (geo.tiles_w + g.strip_tiles_w - 1) / g.strip_tiles_w;
+		g.c_blocks = (geo.channels + f43::kChannelBlock - 1) / f43::kChannelBlock;
+		g.stage_bytes = box_h * g.box_w * f43::kChannelBlock * static_cast<int>(sizeof(T));
+		g.nb_tiles = geo.nb_tiles();
+		const long long items = static_cast<long long>(geo.batch) * g.row_groups * g.w_segments * g.c_blocks;
+		if (items > 0x7FFFFFFFll)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		g.num_items = static_cast<int>(items);
+
+		CUtensorMap map;
+		const uint64_t dims[4] = { static_cast<uint64_t>(geo.channels), static_cast<uint64_t>(geo.width), static_cast<uint64_t>(geo.height),
+				static_cast<uint64_t>(geo.batch) };
+		const uint64_t strides[3] = { static_cast<uint64_t>(geo.channels) * sizeof(T), static_cast<uint64_t>(geo.width) * geo.channels * sizeof(T),
+				static_cast<uint64_t>(geo.height) * geo.width * geo.channels * sizeof(T) };
+		const uint32_t box[4] = { static_cast<uint32_t>(f43::kChannelBlock), static_cast<uint32_t>(g.box_w), static_cast<uint32_t>(box_h), 1u };
+		if (not umma::make_tensor_map(&map, TmaType<T>::value, 4, const_cast<void*>(xPtr), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+
+		auto kernel = f43::kernel_input_tma<T, MT>;
+		constexpr int ring_budget = 96 * 1024;
+		g.stages = std::max(2, std::min(f43::kMaxStages, ring_budget / g.stage_bytes));
+		const int smem_bytes = g.stages * g.stage_bytes + 128;
+		static bool configured[kMaxDevices] = { };
+		if (not configured[ctx.device])
+		{
+			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + 128) != cudaSuccess)
+				return checkForErrors();
+			configured[ctx.device] = true;
+		}
+		int sms = 148;
+		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
+		const int threads = 32 * std::min(8, g.strip_tiles_h * g.strip_tiles_w);
+		const int ctas_per_sm = std::max(1, std::min(3, (220 * 1024) / (smem_bytes + 1024)));
+		const int grid = std::min(g.num_items, ctas_per_sm * sms);
+		kernel<<<grid, threads, smem_bytes, ctx.getStream()>>>(map, reinterpret_cast<MT*>(matricesPtr), g, ctx.getDeviceStatus());
+		return checkForErrors();
+	}
+
+	f43::PlaneGeometry plane_geometry(const ConvGeometry &geo)
+	{
+		f43::PlaneGeometry g;
+		g.batch = geo.batch;
+		g.height = geo.height;
+		g.width = geo.width;
+		g.channels = geo.channels;
+		g.tiles_h = geo.tiles_h;
+		g.tiles_w = geo.tiles_w;
+		g.nb_tiles = geo.nb_tiles();
+		return g;
+	}
+
+	template<typename T, typename MT>
+	avStatus_t launch_f43_output(ContextObject &ctx, const ConvGeometry &geo, const void *matricesPtr, void *yPtr, const void *bPtr, const void *zPtr,
+			float alpha1, float alpha2, float beta, avActivationType_t activation)
+	{
+		if (geo.channels % 2 != 0 or not aligned_to(matricesPtr, 2 * sizeof(MT)) or not aligned_to(yPtr, 2 * sizeof(T))
+				or (zPtr != nullptr and not aligned_to(zPtr, 2 * sizeof(T))) or (bPtr != nullptr and not aligned_to(bPtr, 8)))
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		if (static_cast<long long>(geo.height) * geo.width * geo.channels > 0x7FFFFFFFll)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		const f43::PlaneGeometry g = plane_geometry(geo);
+		if (g.nb_tiles > 0x7FFFFFFFll or geo.channels > 65535 * f43::kChannelBlock)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		const dim3 grid(static_cast<unsigned int>((g.nb_tiles + 7) / 8), (geo.channels + f43::kChannelBlock - 1) / f43::kChannelBlock);
+		const MT *m = reinterpret_cast<const MT*>(matricesPtr);
+		T *y = reinterpret_cast<T*>(yPtr);
+		const float *b = reinterpret_cast<const float*>(bPtr);
+		const T *z = reinterpret_cast<const T*>(zPtr);
+		cudaStream_t stream = ctx.getStream();
+		if (activation == AVOCADO_ACTIVATION_LINEAR)
+			f43::kernel_output<T, MT, 0> <<<grid, f43::kThreads, 0, stream>>>(m, y, g, b, z, alpha1, alpha2, beta, activation);
+		else if (activation == AVOCADO_ACTIVATION_RELU)
+			f43::kernel_output<T, MT, 1> <<<grid, f43::kThreads, 0, stream>>>(m, y, g, b, z, alpha1, alpha2, beta, activation);
+		else
+			f43::kernel_output<T, MT, 2> <<<grid, f43::kThreads, 0, stream>>>(m, y, g, b, z, alpha1, alpha2, beta, activation);
+		return checkForErrors();
+	}
+
+	template<typename T, typename MT>
+	avStatus_t launch_f43_gradient(ContextObject &ctx, const ConvGeometry &geo, const void *dyPtr, void *matricesPtr)
+	{
+		if (geo.channels % 2 != 0 or not aligned_to(matricesPtr, 2 * sizeof(MT)) or not aligned_to(dyPtr, 2 * sizeof(T)))
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		if (static_cast<long long>(geo.height) * geo.width * geo.channels > 0x7FFFFFFFll)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		const f43::PlaneGeometry g = plane_geometry(geo);
+		if (g.nb_tiles > 0x7FFFFFFFll or geo.channels > 65535 * f43::kChannelBlock)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		const dim3 grid(static_cast<unsigned int>((g.nb_tiles + 7) / 8), (geo.channels + f43::kChannelBlock - 1) / f43::kChannelBlock);
+		f43::kernel_gradient<T, MT> <<<grid, f43::kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(dyPtr), g);
+		return checkForErrors();
+	}
+
+	/* the generic kernels stay reachable for A/B comparison: AVOCADO_B200_WINOGRAD=generic disables the fast paths */
+	bool fast_paths_enabled()
+	{
+		static const bool enabled = []()
+		{
+			const char *env = std::getenv("AVOCADO_B200_WINOGRAD");
+			return not (env != nullptr and std::strcmp(env, "generic") == 0);
+		}();
+		return enabled;
+	}
+
+
+	/* float64 has no fast kernel: these wrappers keep the double instantiations out of the fast templates */
+	template<typename T, typename MT>
+	avStatus_t launch_f43_input_if(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr)
+	{
+		if constexpr (sizeof(T) <= 4)
+			return launch_f43_input<T, MT>(ctx, config, geo, xPtr, matricesPtr);
+		else
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+	}
+	template<typename T, typename MT>
+	avStatus_t launch_f43_output_if(ContextObject &ctx, const ConvGeometry &geo, const void *matricesPtr, void *yPtr, const void *bPtr, const void *zPtr,
+			double alpha1, double alpha2, double beta, avActivationType_t activation)
+	{
+		if constexpr (sizeof(T) <= 4)
+			return launch_f43_output<T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, static_cast<float>(alpha1), static_cast<float>(alpha2),
+					static_cast<float>(beta), activation);
+		else
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+	}
+	template<typename T, typename MT>
+	avStatus_t launch_f43_gradient_if(ContextObject &ctx, const ConvGeometry &geo, const void *dyPtr, void *matricesPtr)
+	{
+		if constexpr (sizeof(T) <= 4)
+			return launch_f43_gradient<T, MT>(ctx, geo, dyPtr, matricesPtr);
+		else
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+	}
+
 	template<typename T, typename MT>
 	avStatus_t launch_input_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const TensorObject &xDesc,
 			const void *xPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize)
@@ -423,6 +605,12 @@ namespace
 			return AVOCADO_STATUS_BAD_PARAM;
 		if (geo.nb_tiles() == 0 or geo.channels == 0)
 			return AVOCADO_STATUS_SUCCESS;
+		if (transformSize == 4 and ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
+		{
+			const avStatus_t fast = launch_f43_input_if<T, MT>(ctx, config, geo, xPtr, matricesPtr);
+			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
+				return fast;
+		}
 		const CT padding_value = static_cast<CT>(to_compute(config.getPaddingValue<T>()));
 		const int vec = pick_vec<T, MT>(geo.channels, sizeof(T) == 8 ? 1 : 2, { xPtr }, { matricesPtr });
 		const unsigned int grid = blocks_for(geo.nb_tiles() * (geo.channels / vec));
@@ -443,6 +631,12 @@ namespace
 			return AVOCADO_STATUS_BAD_PARAM;
 		if (geo.nb_tiles() == 0 or geo.channels == 0)
 			return AVOCADO_STATUS_SUCCESS;
+		if (transformSize == 4 and ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
+		{
+			const avStatus_t fast = launch_f43_gradient_if<T, MT>(ctx, geo, dyPtr, matricesPtr);
+			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
+				return fast;
+		}
 		const int vec = pick_vec<T, MT>(geo.channels, sizeof(T) == 8 ? 1 : 2, { dyPtr }, { matricesPtr });
 		const unsigned int grid = blocks_for(geo.nb_tiles() * (geo.channels / vec));
 		DISPATCH_TILE(ks, transformSize,
@@ -467,6 +661,12 @@ namespace
 		const CT a1 = getAlphaValue<CT>(alpha1);
 		const CT a2 = getAlphaValue<CT>(alpha2);
 		const CT b = getBetaValue<CT>(beta);
+		if (transformSize == 4 and ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
+		{
+			const avStatus_t fast = launch_f43_output_if<T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, a1, a2, b, activation);
+			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
+				return fast;
+		}
 		const int vec = pick_vec<T, MT>(geo.channels, sizeof(T) == 8 ? 1 : 2, { yPtr, zPtr }, { matricesPtr });
 		const unsigned int grid = blocks_for(geo.nb_tiles() * (geo.channels / vec));
 		DISPATCH_TILE(ks, transformSize,

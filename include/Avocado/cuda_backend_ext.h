@@ -39,6 +39,16 @@ DLL_PUBLIC avStatus_t cudaGetContextStream(avContextDescriptor_t context, void *
  * whose kernels have no device-side waits. */
 DLL_PUBLIC avStatus_t cudaGetLastDeviceStatus(avContextDescriptor_t context, int *result);
 
+/* Records the work that API calls enqueue on a context instead of running it, and replays it later with one launch.
+ * Between Begin and End every call on `context` is captured into a CUDA graph; host scalars (alpha, beta) are read at
+ * capture time and baked in; the memory handles used must stay alive while the graph exists.  Run the same call
+ * sequence once before capturing, so that one-time set-up (kernel attributes, scratch allocation) is already done.
+ * The default context cannot capture.  No counterpart in the reference, which launches kernel by kernel. */
+DLL_PUBLIC avStatus_t cudaContextBeginCapture(avContextDescriptor_t context);
+DLL_PUBLIC avStatus_t cudaContextEndCapture(avContextDescriptor_t context, av_int64 *graph);
+DLL_PUBLIC avStatus_t cudaContextLaunchGraph(avContextDescriptor_t context, av_int64 graph);
+DLL_PUBLIC avStatus_t cudaDestroyCapturedGraph(av_int64 graph);
+
 #ifdef __cplusplus
 		} /* extern "C" */
 	} /* namespace backend */
