@@ -1,9 +1,585 @@
+/*
+ * conv_implicit_gemm_tc.cu -- implicit-GEMM convolution on the Blackwell tensor cores.
+ *
+ * Counterpart of the reference's kernel_conv_implicit_gemm (src/conv2d_implicit_gemm.cu:150-289), which was meant to
+ * compute a 3x3 convolution as a GEMM with the im2col matrix formed on the fly (dp4a for int8) and was left
+ * unfinished.  Here:
+ *
+ *   GEMM view     rows = output pixels (N*Ho*Wo), columns = filters K, contraction = taps x channels (kh*kw*C)
+ *   A operand     never materialised: for each (tap, channel block) a TMA copy in im2col mode gathers 128
+ *                 consecutive output pixels' input vectors (128 bytes each) straight from the NHWC tensor into
+ *                 128-byte-swizzled shared memory; pixels that fall outside the image arrive as zeros (= padding)
+ *   B operand     the filters [K, kh*kw*C], already contiguous along the contraction: tiled TMA copy
+ *   MMA           tcgen05.mma cta_group::1, M = 128, N = 64/128/256; kind::i8 with int32 accumulation for int8,
+ *                 kind::f16 with float32 accumulation for float16 / bfloat16; accumulator double-buffered in TMEM
+ *   epilogue      four warps drain TMEM: + bias, (requantisation | alpha/z/activation/beta), 16-byte stores
+ *
+ * Roofline: with C = K = 256 the contraction is 2*9*C*K = 1.18 MFLOP per output pixel against 512 bytes moved, so
+ * the kernel is bound by the tensor pipe, not by HBM.
+ */
 #include "conv_kernels.hpp"
-namespace bk
+#include "umma.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <type_traits>
+
+namespace
 {
-	avocado::backend::avStatus_t launch_implicit_gemm_tc(avocado::backend::b200::ContextObject &, const ConvArgs &, avocado::backend::avDataType_t,
-			avocado::backend::avDataType_t, const void *, const void *, const void *)
+	using namespace avocado::backend;
+	using namespace avocado::backend::b200;
+	using namespace bk;
+
+	constexpr int kBlockM = 128;
+	constexpr int kBlockKBytes = 128;
+	constexpr int kThreads = 192;
+
+	struct IgParams
 	{
-		return avocado::backend::AVOCADO_STATUS_NOT_SUPPORTED;
+			int pixels; /* N * Ho * Wo */
+			int filters, channels;
+			int out_h, out_w;
+			int pad_h, pad_w;
+			int kernel_h, kernel_w;
+			int rotate;
+			int m_blocks, n_blocks, c_blocks, k_blocks;
+			int num_tiles;
+			const void *bias;
+			const float *scales;
+			const void *z;
+			void *y;
+			float alpha1, alpha2, beta;
+			int activation;
+			int int8_output;
+	};
+
+	template<typename T> struct Element;
+	template<> struct Element<int8_t>
+	{
+			static constexpr bool kInteger = true;
+			static constexpr uint32_t kFormat = umma::kFormatS8;
+			static constexpr uint32_t kAccum = umma::kAccumS32;
+			static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+	};
+	template<> struct Element<half>
+	{
+			static constexpr bool kInteger = false;
+			static constexpr uint32_t kFormat = umma::kFormatF16;
+			static constexpr uint32_t kAccum = umma::kAccumF32;
+			static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+	};
+	template<> struct Element<__nv_bfloat16>
+	{
+			static constexpr bool kInteger = false;
+			static constexpr uint32_t kFormat = umma::kFormatBF16;
+			static constexpr uint32_t kAccum = umma::kAccumF32;
+			static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+	};
+
+	template<int BLOCK_N, int STAGES>
+	struct IgConfig
+	{
+			static constexpr int kABytes = kBlockM * kBlockKBytes;
+			static constexpr int kBBytes = BLOCK_N * kBlockKBytes;
+			static constexpr int kStageBytes = kABytes + kBBytes;
+			static constexpr int kSmemBytes = STAGES * kStageBytes + 1024;
+			static constexpr int kTmemColumns = 2 * BLOCK_N;
+	};
+
+	__device__ __forceinline__ uint32_t pack_half2(float a, float b, half)
+	{
+		__half2 v = __floats2half2_rn(a, b);
+		return *reinterpret_cast<uint32_t*>(&v);
+	}
+	__device__ __forceinline__ uint32_t pack_half2(float a, float b, __nv_bfloat16)
+	{
+		__nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+		return *reinterpret_cast<uint32_t*>(&v);
+	}
+	__device__ __forceinline__ float2 unpack_half2(uint32_t raw, half)
+	{
+		return __half22float2(*reinterpret_cast<__half2*>(&raw));
+	}
+	__device__ __forceinline__ float2 unpack_half2(uint32_t raw, __nv_bfloat16)
+	{
+		return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw));
+	}
+
+	template<typename T, int BLOCK_N, int STAGES>
+	__global__ void __launch_bounds__(kThreads, 1) kernel_implicit_gemm_tc(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW,
+			IgParams p, int *deviceStatus)
+	{
+		using Cfg = IgConfig<BLOCK_N, STAGES>;
+		constexpr int kElemsPerBlock = kBlockKBytes / static_cast<int>(sizeof(T)); /* channels per contraction block */
+		constexpr int kMmaK = 32 / static_cast<int>(sizeof(T)); /* elements consumed by one tcgen05.mma */
+		extern __shared__ uint8_t smem_raw[];
+		uint8_t *smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+		__shared__ __align__(8) uint64_t full_bar[STAGES];
+		__shared__ __align__(8) uint64_t empty_bar[STAGES];
+		__shared__ __align__(8) uint64_t tmem_full_bar[2];
+		__shared__ __align__(8) uint64_t tmem_empty_bar[2];
+		__shared__ uint32_t tmem_base_slot;
+		__shared__ int abort_flag;
+		__shared__ volatile int epilogue_go;
+		__shared__ float scale_s[BLOCK_N];
+		__shared__ float bias_s[BLOCK_N]; /* int32 bit patterns in the integer case */
+
+		const int warp = threadIdx.x / 32;
+		const int lane = threadIdx.x % 32;
+
+		if (threadIdx.x == 0)
+		{
+			abort_flag = 0;
+			for (int s = 0; s < STAGES; s++)
+			{
+				umma::mbar_init(&full_bar[s], 1);
+				umma::mbar_init(&empty_bar[s], 1);
+			}
+			for (int a = 0; a < 2; a++)
+			{
+				umma::mbar_init(&tmem_full_bar[a], 1);
+				umma::mbar_init(&tmem_empty_bar[a], 128);
+			}
+			umma::mbar_fence_init();
+			umma::prefetch_tensormap(&mapX);
+			umma::prefetch_tensormap(&mapW);
+		}
+		if (warp == 1)
+		{
+			umma::tmem_alloc(&tmem_base_slot, Cfg::kTmemColumns);
+			umma::tmem_relinquish();
+		}
+		umma::tcgen05_fence_before();
+		__syncthreads();
+		umma::tcgen05_fence_after();
+		const uint32_t tmem_base = tmem_base_slot;
+		volatile int *abort_ptr = &abort_flag;
+		const int taps = p.kernel_h * p.kernel_w;
+
+		if (warp == 0)
+		{
+			if (lane == 0)
+			{
+				int stage = 0;
+				uint32_t phase = 0;
+				bool ok = true;
+				const int image = p.out_h * p.out_w;
+				for (int tile = blockIdx.x; tile < p.num_tiles and ok; tile += gridDim.x)
+				{
+					const int nb = tile % p.n_blocks;
+					const int mb = tile / p.n_blocks;
+					const int m0 = mb * kBlockM;
+					const int n = m0 / image;
+					const int rem = m0 - n * image;
+					const int oh = rem / p.out_w;
+					const int ow = rem - oh * p.out_w;
+					for (int kb = 0; kb < p.k_blocks; kb++)
+					{
+						const int tap = kb / p.c_blocks;
+						const int cb = kb - tap * p.c_blocks;
+						const int r = tap / p.kernel_w;
+						const int s = tap - r * p.kernel_w;
+						const int wtap = p.rotate ? (taps - 1 - tap) : tap;
+						if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
+						{
+							umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
+							ok = false;
+							break;
+						}
+						uint8_t *a_dst = smem + stage * Cfg::kStageBytes;
+						uint8_t *b_dst = a_dst + Cfg::kABytes;
+						umma::mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+						umma::tma_load_im2col_4d(a_dst, &mapX, &full_bar[stage], cb * kElemsPerBlock, ow + p.pad_w, oh + p.pad_h, n, static_cast<uint16_t>(s),
+								static_cast<uint16_t>(r));
+						umma::tma_load_2d(b_dst, &mapW, &full_bar[stage], wtap * p.channels + cb * kElemsPerBlock, nb * BLOCK_N);
+						if (++stage == STAGES)
+						{
+							stage = 0;
+							phase ^= 1u;
+						}
+					}
+				}
+			}
+		}
+		else if (warp == 1)
+		{
+			if (lane == 0)
+			{
+				constexpr uint32_t idesc = umma::make_instr_desc(Element<T>::kAccum, Element<T>::kFormat, Element<T>::kFormat, false, false, kBlockM, BLOCK_N);
+				int stage = 0;
+				uint32_t phase = 0;
+				int it = 0;
+				bool ok = true;
+				for (int tile = blockIdx.x; tile < p.num_tiles and ok; tile += gridDim.x, it++)
+				{
+					const int acc = it & 1;
+					const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
+					if (not umma::mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_ptr))
+					{
+						umma::raise_error(abort_ptr, deviceStatus, umma::kErrorMmaWait);
+						break;
+					}
+					umma::tcgen05_fence_after();
+					const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+					for (int kb = 0; kb < p.k_blocks; kb++)
+					{
+						if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
+						{
+							umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
+							ok = false;
+							break;
+						}
+						umma::tcgen05_fence_after();
+						const uint32_t a_addr = umma::smem_u32(smem + stage * Cfg::kStageBytes);
+						const uint32_t b_addr = a_addr + Cfg::kABytes;
+						const uint64_t a_desc = umma::make_smem_desc(a_addr, 16, 1024, umma::kSwizzle128B);
+						const uint64_t b_desc = umma::make_smem_desc(b_addr, 16, 1024, umma::kSwizzle128B);
+#pragma unroll
+						for (int k = 0; k < kElemsPerBlock / kMmaK; k++)
+						{
+							/* one MMA consumes 32 bytes of every row: +2 in descriptor units */
+							if constexpr (Element<T>::kInteger)
+								umma::mma_i8(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
+							else
+								umma::mma_f16(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
+						}
+						umma::mma_commit(&empty_bar[stage]);
+						if (++stage == STAGES)
+						{
+							stage = 0;
+							phase ^= 1u;
+						}
+					}
+					if (ok)
+						umma::mma_commit(&tmem_full_bar[acc]);
+				}
+			}
+		}
+		else
+		{
+			const int quarter = warp % 4;
+			const int row = quarter * 32 + lane;
+			const int epi_thread = threadIdx.x - 64;
+			const avActivationType_t activation = static_cast<avActivationType_t>(p.activation);
+			int it = 0;
+			int staged_nb = -1;
+			for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, it++)
+			{
+				const int nb = tile % p.n_blocks;
+				const int mb = tile / p.n_blocks;
+				const int acc = it & 1;
+				const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
+				const int k0 = nb * BLOCK_N;
+
+				/* per-filter scale and bias of this column block: staged once per change of block */
+				if (staged_nb != nb)
+				{
+					if (staged_nb >= 0)
+						umma::named_barrier_sync(1, 128); /* nobody still reads the previous block's values */
+					for (int j = epi_thread; j < BLOCK_N; j += 128)
+					{
+						const int k = k0 + j;
+						float sc = 1.0f, bi = 0.0f;
+						if (k < p.filters)
+						{
+							if (p.scales != nullptr)
+								sc = p.scales[k];
+							if (p.bias != nullptr)
+								bi = reinterpret_cast<const float*>(p.bias)[k]; /* float, or int32 bit pattern */
+						}
+						scale_s[j] = sc;
+						bias_s[j] = bi;
+					}
+					staged_nb = nb;
+				}
+				if (epi_thread == 0)
+				{
+					const bool ready = umma::mbar_wait(&tmem_full_bar[acc], acc_phase, abort_ptr);
+					if (not ready)
+						umma::raise_error(abort_ptr, deviceStatus, umma::kErrorEpilogueWait);
+					epilogue_go = ready ? 1 : 0;
+				}
+				umma::named_barrier_sync(1, 128);
+				if (epilogue_go == 0)
+					break;
+				umma::tcgen05_fence_after();
+
+				const int m = mb * kBlockM + row;
+				const bool row_valid = m < p.pixels;
+				const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
+#pragma unroll 1
+				for (int chunk = 0; chunk < BLOCK_N / 32; chunk++)
+				{
+					uint32_t r[32];
+					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(chunk * 32), r);
+					umma::tmem_load_wait();
+					const int kc = k0 + chunk * 32; /* first filter of this chunk */
+					if (not row_valid or kc >= p.filters)
+						continue;
+					const size_t index = static_cast<size_t>(m) * p.filters + kc;
+					if constexpr (Element<T>::kInteger)
+					{
+						if (p.int8_output)
+						{
+							const int8_t *z = reinterpret_cast<const int8_t*>(p.z);
+							uint32_t packed[8];
+#pragma unroll
+							for (int w = 0; w < 8; w++)
+							{
+								uint32_t word = 0;
+#pragma unroll
+								for (int b = 0; b < 4; b++)
+								{
+									const int j = w * 4 + b;
+									const int32_t t = static_cast<int32_t>(r[j]) + __float_as_int(bias_s[chunk * 32 + j]);
+									float v = __int2float_rn(t);
+									if (p.alpha1 != 1.0f)
+										v = __fmul_rn(p.alpha1, v);
+									if (p.scales != nullptr)
+										v = __fmul_rn(v, scale_s[chunk * 32 + j]);
+									if (z != nullptr)
+										v = __fadd_rn(v, __fmul_rn(p.alpha2, static_cast<float>(z[index + j])));
+									if (activation == AVOCADO_ACTIVATION_RELU)
+										v = fmaxf(v, 0.0f);
+									else if (activation != AVOCADO_ACTIVATION_LINEAR)
+										v = activation_forward(activation, v);
+									int32_t q;
+									asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
+									word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+								}
+								packed[w] = word;
+							}
+							int8_t *dst = reinterpret_cast<int8_t*>(p.y) + index;
+							if (kc + 16 <= p.filters)
+								*reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+							if (kc + 32 <= p.filters)
+								*reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+						}
+						else
+						{
+							int32_t *dst = reinterpret_cast<int32_t*>(p.y) + index;
+#pragma unroll
+							for (int w = 0; w < 8; w++)
+								if (kc + 4 * w + 4 <= p.filters)
+								{
+									uint4 out;
+									out.x = static_cast<uint32_t>(static_cast<int32_t>(r[4 * w + 0]) + __float_as_int(bias_s[chunk * 32 + 4 * w + 0]));
+									out.y = static_cast<uint32_t>(static_cast<int32_t>(r[4 * w + 1]) + __float_as_int(bias_s[chunk * 32 + 4 * w + 1]));
+									out.z = static_cast<uint32_t>(static_cast<int32_t>(r[4 * w + 2]) + __float_as_int(bias_s[chunk * 32 + 4 * w + 2]));
+									out.w = static_cast<uint32_t>(static_cast<int32_t>(r[4 * w + 3]) + __float_as_int(bias_s[chunk * 32 + 4 * w + 3]));
+									*reinterpret_cast<uint4*>(dst + 4 * w) = out;
+								}
+						}
+					}
+					else
+					{
+						/* 16-bit floating tensors: 32 results = 64 bytes = 4 stores of 8 elements */
+						using H = T;
+						H *dst = reinterpret_cast<H*>(p.y) + index;
+						const H *z = reinterpret_cast<const H*>(p.z);
+#pragma unroll
+						for (int w = 0; w < 4; w++)
+						{
+							if (kc + 8 * w + 8 > p.filters)
+								continue;
+							uint4 zraw = make_uint4(0, 0, 0, 0), yraw = make_uint4(0, 0, 0, 0);
+							if (z != nullptr)
+								zraw = *reinterpret_cast<const uint4*>(z + index + 8 * w);
+							if (p.beta != 0.0f)
+								yraw = *reinterpret_cast<const uint4*>(dst + 8 * w);
+							const uint32_t zw[4] = { zraw.x, zraw.y, zraw.z, zraw.w };
+							const uint32_t yw[4] = { yraw.x, yraw.y, yraw.z, yraw.w };
+							uint32_t out[4];
+#pragma unroll
+							for (int q = 0; q < 4; q++)
+							{
+								const int j = 8 * w + 2 * q;
+								float v0 = fmaf(p.alpha1, __uint_as_float(r[j]), bias_s[chunk * 32 + j]);
+								float v1 = fmaf(p.alpha1, __uint_as_float(r[j + 1]), bias_s[chunk * 32 + j + 1]);
+								if (z != nullptr)
+								{
+									const float2 zz = unpack_half2(zw[q], H());
+									v0 = fmaf(p.alpha2, zz.x, v0);
+									v1 = fmaf(p.alpha2, zz.y, v1);
+								}
+								if (activation == AVOCADO_ACTIVATION_RELU)
+								{
+									v0 = fmaxf(v0, 0.0f);
+									v1 = fmaxf(v1, 0.0f);
+								}
+								else if (activation != AVOCADO_ACTIVATION_LINEAR)
+								{
+									v0 = activation_forward(activation, v0);
+									v1 = activation_forward(activation, v1);
+								}
+								if (p.beta != 0.0f)
+								{
+									const float2 yy = unpack_half2(yw[q], H());
+									v0 = fmaf(p.beta, yy.x, v0);
+									v1 = fmaf(p.beta, yy.y, v1);
+								}
+								out[q] = pack_half2(v0, v1, H());
+							}
+							*reinterpret_cast<uint4*>(dst + 8 * w) = make_uint4(out[0], out[1], out[2], out[3]);
+						}
+					}
+				}
+				/* accumulator drained: hand it back to the MMA warp */
+				umma::tcgen05_fence_before();
+				umma::mbar_arrive(&tmem_empty_bar[acc]);
+			}
+		}
+
+		__syncthreads();
+		if (abort_flag != 0)
+			umma::drain_after_abort();
+		if (warp == 1)
+		{
+			umma::tcgen05_fence_after();
+			umma::tmem_dealloc(tmem_base, Cfg::kTmemColumns);
+		}
+	}
+
+	template<typename T, int BLOCK_N, int STAGES>
+	avStatus_t launch_config(ContextObject &ctx, const CUtensorMap &mapX, const CUtensorMap &mapW, IgParams &p)
+	{
+		using Cfg = IgConfig<BLOCK_N, STAGES>;
+		auto kernel = kernel_implicit_gemm_tc<T, BLOCK_N, STAGES>;
+		static bool configured[kMaxDevices] = { };
+		if (not configured[ctx.device])
+		{
+			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+				return checkForErrors();
+			configured[ctx.device] = true;
+		}
+		p.n_blocks = (p.filters + BLOCK_N - 1) / BLOCK_N;
+		const long long tiles = static_cast<long long>(p.m_blocks) * p.n_blocks;
+		if (tiles > 0x7FFFFFFFll)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		p.num_tiles = static_cast<int>(tiles);
+		int sms = 148;
+		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
+		const int grid = std::min(p.num_tiles, sms);
+		kernel<<<grid, kThreads, Cfg::kSmemBytes, ctx.getStream()>>>(mapX, mapW, p, ctx.getDeviceStatus());
+		return checkForErrors();
+	}
+
+	bool tensor_cores_enabled()
+	{
+		static const bool enabled = []()
+		{
+			const char *env = std::getenv("AVOCADO_B200_CONV");
+			return not (env != nullptr and std::strcmp(env, "direct") == 0);
+		}();
+		return enabled;
+	}
+
+	template<typename T>
+	avStatus_t launch_typed(ContextObject &ctx, const ConvArgs &args, avDataType_t yType, const void *alpha1, const void *alpha2, const void *beta)
+	{
+		const int elem = static_cast<int>(sizeof(T));
+		const int block_channels = kBlockKBytes / elem;
+		/* shapes the kernel covers; everything else goes to the direct kernel */
+		if (args.channels % block_channels != 0)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		const int out_align = Element<T>::kInteger ? 16 : 8;
+		if (args.filters % out_align != 0 or args.filters < 16)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		if (args.kernel_h > 16 or args.kernel_w > 16 or args.kernel_h * args.kernel_w > 64)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		const long long pixels = static_cast<long long>(args.batch) * args.out_height * args.out_width;
+		if (pixels == 0)
+			return AVOCADO_STATUS_SUCCESS;
+		if (pixels > 0x7FFFFF00ll)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		/* bounding box of the im2col map: base pixels run from pad to pad + out - 1 */
+		const int lower[2] = { args.pad_w, args.pad_h };
+		const int upper[2] = { args.out_width - args.width + args.pad_w, args.out_height - args.height + args.pad_h };
+		for (int i = 0; i < 2; i++)
+			if (lower[i] < -128 or lower[i] > 127 or upper[i] < -128 or upper[i] > 127)
+				return AVOCADO_STATUS_NOT_SUPPORTED;
+		/* im2col maps of tensors below 128 KB are avoided: small problems do not need this kernel */
+		const long long x_bytes = static_cast<long long>(args.batch) * args.height * args.width * args.channels * elem;
+		if (x_bytes < 131072)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		if (reinterpret_cast<uintptr_t>(args.x) % 16 != 0 or reinterpret_cast<uintptr_t>(args.w) % 16 != 0 or reinterpret_cast<uintptr_t>(args.y) % 16 != 0
+				or (args.z != nullptr and reinterpret_cast<uintptr_t>(args.z) % 16 != 0))
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+
+		CUtensorMap mapX, mapW;
+		{
+			const uint64_t dims[4] = { static_cast<uint64_t>(args.channels), static_cast<uint64_t>(args.width), static_cast<uint64_t>(args.height),
+					static_cast<uint64_t>(args.batch) };
+			const uint64_t strides[3] = { static_cast<uint64_t>(args.channels) * elem, static_cast<uint64_t>(args.width) * args.channels * elem,
+					static_cast<uint64_t>(args.height) * args.width * args.channels * elem };
+			if (not umma::make_im2col_map(&mapX, Element<T>::kTma, const_cast<void*>(args.x), dims, strides, lower, upper, block_channels, kBlockM,
+					CU_TENSOR_MAP_SWIZZLE_128B))
+				return AVOCADO_STATUS_NOT_SUPPORTED;
+		}
+		const int taps = args.kernel_h * args.kernel_w;
+		const int block_n = (args.filters <= 64) ? 64 : (args.filters <= 128) ? 128 : 256;
+		{
+			const uint64_t dims[2] = { static_cast<uint64_t>(taps) * args.channels, static_cast<uint64_t>(args.filters) };
+			const uint64_t strides[1] = { static_cast<uint64_t>(taps) * args.channels * elem };
+			const uint32_t box[2] = { static_cast<uint32_t>(block_channels), static_cast<uint32_t>(block_n) };
+			if (not umma::make_tensor_map(&mapW, Element<T>::kTma, 2, const_cast<void*>(args.w), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+				return AVOCADO_STATUS_NOT_SUPPORTED;
+		}
+
+		IgParams p;
+		p.pixels = static_cast<int>(pixels);
+		p.filters = args.filters;
+		p.channels = args.channels;
+		p.out_h = args.out_height;
+		p.out_w = args.out_width;
+		p.pad_h = args.pad_h;
+		p.pad_w = args.pad_w;
+		p.kernel_h = args.kernel_h;
+		p.kernel_w = args.kernel_w;
+		p.rotate = args.rotate_kernel ? 1 : 0;
+		p.m_blocks = static_cast<int>((pixels + kBlockM - 1) / kBlockM);
+		p.c_blocks = args.channels / block_channels;
+		p.k_blocks = taps * p.c_blocks;
+		p.bias = args.bias;
+		p.scales = reinterpret_cast<const float*>(args.scales);
+		p.z = args.z;
+		p.y = args.y;
+		p.alpha1 = getAlphaValue<float>(alpha1);
+		p.alpha2 = getAlphaValue<float>(alpha2);
+		p.beta = getBetaValue<float>(beta);
+		p.activation = static_cast<int>(args.activation);
+		p.int8_output = (yType == AVOCADO_DTYPE_INT8) ? 1 : 0;
+		switch (block_n)
+		{
+			case 64:
+				return launch_config<T, 64, 6>(ctx, mapX, mapW, p);
+			case 128:
+				return launch_config<T, 128, 5>(ctx, mapX, mapW, p);
+			default:
+				return launch_config<T, 256, 4>(ctx, mapX, mapW, p);
+		}
 	}
 }
+
+namespace bk
+{
+	avStatus_t launch_implicit_gemm_tc(ContextObject &ctx, const ConvArgs &args, avDataType_t xType, avDataType_t yType, const void *alpha1,
+			const void *alpha2, const void *beta)
+	{
+		if (not tensor_cores_enabled() or cuda_sm_version(ctx.device) != 100)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		switch (xType)
+		{
+			case AVOCADO_DTYPE_INT8:
+				return launch_typed<int8_t>(ctx, args, yType, alpha1, alpha2, beta);
+			case AVOCADO_DTYPE_FLOAT16:
+				return launch_typed<half>(ctx, args, yType, alpha1, alpha2, beta);
+			case AVOCADO_DTYPE_BFLOAT16:
+				return launch_typed<__nv_bfloat16>(ctx, args, yType, alpha1, alpha2, beta);
+			default:
+				return AVOCADO_STATUS_NOT_SUPPORTED;
+		}
+	}
+} /* namespace bk */

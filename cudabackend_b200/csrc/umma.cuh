@@ -129,6 +129,21 @@ namespace umma
 		asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
 				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 	}
+	__device__ __forceinline__ void tma_load_2d(void *smemDst, const CUtensorMap *map, uint64_t *bar, int c0, int c1)
+	{
+		asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+	}
+	/* im2col mode over an NHWC tensor: (c, w, h, n) is the first base pixel (in input coordinates, may be negative
+	 * inside the bounding box of the map), (offW, offH) the filter tap added to every base pixel; the copy walks
+	 * pixelsPerColumn base pixels along w, then h, then n, and delivers channelsPerPixel channels of each. */
+	__device__ __forceinline__ void tma_load_im2col_4d(void *smemDst, const CUtensorMap *map, uint64_t *bar, int c, int w, int h, int n, uint16_t offW,
+			uint16_t offH)
+	{
+		asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(offW), "h"(offH)
+				: "memory");
+	}
 	__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *smemSrc, int c0, int c1, int c2)
 	{
 		asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
@@ -281,6 +296,41 @@ namespace umma
 		}
 		const CUresult status = fn(map, dtype, static_cast<cuuint32_t>(rank), base, gdims, gstrides, gbox, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
 				CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+		return status == CUDA_SUCCESS;
+	}
+
+	typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+			cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+	inline EncodeIm2colFn encode_im2col_fn()
+	{
+		static EncodeIm2colFn fn = []() -> EncodeIm2colFn
+		{
+			void *ptr = nullptr;
+			cudaDriverEntryPointQueryResult result;
+			if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &ptr, cudaEnableDefault, &result) != cudaSuccess or result != cudaDriverEntryPointSuccess)
+			{
+				cudaGetLastError();
+				return nullptr;
+			}
+			return reinterpret_cast<EncodeIm2colFn>(ptr);
+		}();
+		return fn;
+	}
+
+	/* im2col map over an NHWC tensor (dims innermost first: C, W, H, N).  lower/upper corner are the offsets of the
+	 * bounding box of base pixels from (0,0) and from (W-1,H-1), in {W, H} order. */
+	inline bool make_im2col_map(CUtensorMap *map, CUtensorMapDataType dtype, void *base, const uint64_t dims[4], const uint64_t stridesBytes[3],
+			const int lowerCorner[2], const int upperCorner[2], uint32_t channelsPerPixel, uint32_t pixelsPerColumn, CUtensorMapSwizzle swizzle)
+	{
+		EncodeIm2colFn fn = encode_im2col_fn();
+		if (fn == nullptr)
+			return false;
+		cuuint64_t gdims[4] = { dims[0], dims[1], dims[2], dims[3] };
+		cuuint64_t gstrides[3] = { stridesBytes[0], stridesBytes[1], stridesBytes[2] };
+		cuuint32_t estrides[4] = { 1, 1, 1, 1 };
+		const CUresult status = fn(map, dtype, 4, base, gdims, gstrides, lowerCorner, upperCorner, channelsPerPixel, pixelsPerColumn, estrides,
+				CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 		return status == CUDA_SUCCESS;
 	}
 } /* namespace umma */

@@ -103,10 +103,12 @@ def test_config3_shape_fused_bf16(ctx):
     assert o.error_metrics(got, ref)["elem"] <= common.TOLERANCE["bfloat16"]
 
 
-def int8_case(ctx, n, h, w, c, k, scale_range, activation="linear", with_z=False, int32_output=False):
-    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "int8", out_dtype="int32" if int32_output else "int8")
+def int8_case(ctx, n, h, w, c, k, scale_range, activation="linear", with_z=False, int32_output=False, ks=3, rotated=False):
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "int8", out_dtype="int32" if int32_output else "int8", kernel_size=ks)
+    if rotated:
+        d.conv = api.ConvolutionDescriptor(api.CROSS_CORRELATION_MODE, (-(ks // 2), -(ks // 2)))
     x = common.int8_uniform("x", (n, h, w, c))
-    wt = common.int8_uniform("w", (k, 3, 3, c))
+    wt = common.int8_uniform("w", (k, ks, ks, c))
     bias = common.rng("b").integers(-1000, 1001, k, dtype=np.int32)
     d.x.upload(ctx, x)
     d.wt.upload(ctx, wt)
@@ -121,7 +123,9 @@ def int8_case(ctx, n, h, w, c, k, scale_range, activation="linear", with_z=False
             d.set_z(z)
     d.implicit_gemm(alpha2=0.5 if with_z else None, activation=activation)
     got = d.y.download_raw(ctx)
-    ref = o.conv2d_forward_int8(x, wt, bias, scales, z, alpha2=0.5, activation=activation, int32_output=int32_output)
+    w_eff = np.ascontiguousarray(wt[:, ::-1, ::-1, :]) if rotated else wt
+    pad = -(ks // 2)
+    ref = o.conv2d_forward_int8(x, w_eff, bias, scales, z, padding=(pad, pad), alpha2=0.5, activation=activation, int32_output=int32_output)
     return got, ref
 
 
@@ -160,3 +164,38 @@ def test_int8_round_half_to_even(ctx):
     got = d.y.download_raw(ctx).reshape(-1)
     expect = o.conv2d_forward_int8(x, wt, None, np.full(16, 0.5, dtype=np.float32)).reshape(-1)
     assert got.tolist() == expect.tolist() == [0, 2, 2, 0, -2, 64, -64, 4, 4, 6, -2, -4, 1, 2, 0, 6]
+
+
+@pytest.mark.parametrize("shape", [(8, 14, 14, 128, 64), (3, 20, 17, 256, 96), (16, 7, 9, 384, 272)])
+def test_int8_tensor_core_shapes(ctx, shape):
+    """shapes that take the tcgen05 kernel: ragged pixel counts, K below / between / above the column-block sizes"""
+    n, h, w, c, k = shape
+    got, ref = int8_case(ctx, n, h, w, c, k, (5e-5, 2e-4), activation="relu", with_z=True)
+    assert np.array_equal(got, ref)
+    got, ref = int8_case(ctx, n, h, w, c, k, None, int32_output=True)
+    assert np.array_equal(got, ref)
+
+
+def test_int8_tensor_core_rotated_and_5x5(ctx):
+    got, ref = int8_case(ctx, 8, 14, 14, 128, 64, (5e-5, 2e-4), rotated=True)
+    assert np.array_equal(got, ref)
+    got, ref = int8_case(ctx, 8, 14, 14, 128, 64, (2e-5, 8e-5), ks=5)
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(8, 14, 14, 128, 128), (4, 28, 28, 64, 72), (2, 30, 31, 192, 320)])
+def test_implicit_gemm_tensor_core_16bit(ctx, dtype, shape):
+    n, h, w, c, k = shape
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, dtype)
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+    b = d.set_bias(common.uniform("b", (k,), -0.1, 0.1))
+    z = d.set_z(common.uniform("z", d.y.shape))
+    y0 = d.y.upload(ctx, common.uniform("y", d.y.shape))
+    d.implicit_gemm(alpha1=1.1, alpha2=1.2, beta=0.1, activation="relu")
+    got = d.y.download(ctx)
+    f = lambda v: float(np.float32(v))
+    ref = o.conv2d_forward(x, wt, bias=b, z=z, y=y0, alpha1=f(1.1), alpha2=f(1.2), beta=f(0.1), activation="relu")
+    # float32 accumulation: the error is the rounding of the stored result
+    assert o.error_metrics(got, ref)["elem"] <= {"float16": 1.5e-3, "bfloat16": 1e-2}[dtype]
