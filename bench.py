@@ -240,7 +240,7 @@ class Workload:
     def pin_host_buffers(self, data):
         api = self.api
         stored, _ = api.to_storage(data["x"], self.cfg["dtype"])
-        self.host_x = np.ascontiguousarray(stored)
+        self.host_x = np.array(stored, copy=True, order="C")
         self.host_y = api.host_buffer(self.y_tensor.shape, self.y_tensor.dtype)
         api.call("cudaPageLock", self.host_x.ctypes.data_as(api._VP), self.host_x.nbytes)
         api.call("cudaPageLock", self.host_y.ctypes.data_as(api._VP), self.host_y.nbytes)

@@ -11,11 +11,11 @@
  * channel), defined by this library because the reference's int8 kernel has no requantisation
  * (src/conv2d_implicit_gemm.cu:278, :330-339):
  *     t = acc + b[k]                      int32
- *     r = float(t)                        cvt.rn.f32.s32
+ *     r = float(t)                        round to nearest even, as cvt.rn.f32.s32
  *     r = alpha1 * r   (if alpha1 != 1);  r = r * scale[k]   (if scales are attached)     one rounding each
  *     r = r + alpha2 * float(z)           (if z is given)
  *     r = activation(r)
- *     y = saturate_int8(round_to_nearest_even(r))            cvt.rni.sat.s8.f32
+ *     y = saturate_int8(round_to_nearest_even(r))            as cvt.rni.sat.s8.f32 (NaN saturates to -128)
  * With an int32 y the raw t is stored.
  */
 #ifndef B200_CONV_COMMON_CUH_
@@ -41,20 +41,18 @@ namespace bk
 	__device__ __forceinline__ int8_t requantize(int32_t accPlusBias, float alpha1, bool useAlpha1, const float *scales, int k, const int8_t *z,
 			size_t index, float alpha2, avocado::backend::avActivationType_t activation)
 	{
-		float r = __int2float_rn(accPlusBias);
+		float r = int_to_float_rn(accPlusBias);
 		if (useAlpha1)
 			r = __fmul_rn(alpha1, r);
 		if (scales != nullptr)
 			r = __fmul_rn(r, scales[k]);
 		if (z != nullptr)
-			r = __fadd_rn(r, __fmul_rn(alpha2, static_cast<float>(z[index])));
+			r = __fadd_rn(r, __fmul_rn(alpha2, small_int_to_float(z[index])));
 		if (activation == avocado::backend::AVOCADO_ACTIVATION_RELU)
 			r = fmaxf(r, 0.0f);
 		else if (activation != avocado::backend::AVOCADO_ACTIVATION_LINEAR)
 			r = activation_forward(activation, r);
-		int32_t q;
-		asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(r));
-		return static_cast<int8_t>(q);
+		return static_cast<int8_t>(float_to_int8_rn_sat(r));
 	}
 } /* namespace bk */
 

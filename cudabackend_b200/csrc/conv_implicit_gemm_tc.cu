@@ -33,7 +33,9 @@ namespace
 
 	constexpr int kBlockM = 128;
 	constexpr int kBlockKBytes = 128;
-	constexpr int kThreads = 192;
+	constexpr int kEpilogueWarps = 8;
+	constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+	constexpr int kThreads = 64 + kEpilogueThreads;
 
 	struct IgParams
 	{
@@ -140,7 +142,7 @@ namespace
 			for (int a = 0; a < 2; a++)
 			{
 				umma::mbar_init(&tmem_full_bar[a], 1);
-				umma::mbar_init(&tmem_empty_bar[a], 128);
+				umma::mbar_init(&tmem_empty_bar[a], kEpilogueThreads);
 			}
 			umma::mbar_fence_init();
 			umma::prefetch_tensormap(&mapX);
@@ -259,7 +261,10 @@ namespace
 		}
 		else
 		{
+			/* eight warps: warp w drains TMEM lanes 32*(w%4).. (the only lanes it may read) and, of the BLOCK_N columns,
+			 * the half given by (w-2)/4 */
 			const int quarter = warp % 4;
+			const int column_half = (warp - 2) / 4;
 			const int row = quarter * 32 + lane;
 			const int epi_thread = threadIdx.x - 64;
 			const avActivationType_t activation = static_cast<avActivationType_t>(p.activation);
@@ -277,8 +282,8 @@ namespace
 				if (staged_nb != nb)
 				{
 					if (staged_nb >= 0)
-						umma::named_barrier_sync(1, 128); /* nobody still reads the previous block's values */
-					for (int j = epi_thread; j < BLOCK_N; j += 128)
+						umma::named_barrier_sync(1, kEpilogueThreads); /* nobody still reads the previous block's values */
+					for (int j = epi_thread; j < BLOCK_N; j += kEpilogueThreads)
 					{
 						const int k = k0 + j;
 						float sc = 1.0f, bi = 0.0f;
@@ -301,7 +306,7 @@ namespace
 						umma::raise_error(abort_ptr, deviceStatus, umma::kErrorEpilogueWait);
 					epilogue_go = ready ? 1 : 0;
 				}
-				umma::named_barrier_sync(1, 128);
+				umma::named_barrier_sync(1, kEpilogueThreads);
 				if (epilogue_go == 0)
 					break;
 				umma::tcgen05_fence_after();
@@ -310,7 +315,7 @@ namespace
 				const bool row_valid = m < p.pixels;
 				const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-				for (int chunk = 0; chunk < BLOCK_N / 32; chunk++)
+				for (int chunk = column_half * (BLOCK_N / 64); chunk < (column_half + 1) * (BLOCK_N / 64); chunk++)
 				{
 					uint32_t r[32];
 					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(chunk * 32), r);
@@ -334,20 +339,18 @@ namespace
 								{
 									const int j = w * 4 + b;
 									const int32_t t = static_cast<int32_t>(r[j]) + __float_as_int(bias_s[chunk * 32 + j]);
-									float v = __int2float_rn(t);
+									float v = int_to_float_rn(t);
 									if (p.alpha1 != 1.0f)
 										v = __fmul_rn(p.alpha1, v);
 									if (p.scales != nullptr)
 										v = __fmul_rn(v, scale_s[chunk * 32 + j]);
 									if (z != nullptr)
-										v = __fadd_rn(v, __fmul_rn(p.alpha2, static_cast<float>(z[index + j])));
+										v = __fadd_rn(v, __fmul_rn(p.alpha2, small_int_to_float(z[index + j])));
 									if (activation == AVOCADO_ACTIVATION_RELU)
 										v = fmaxf(v, 0.0f);
 									else if (activation != AVOCADO_ACTIVATION_LINEAR)
-										v = activation_forward(activation, v);
-									int32_t q;
-									asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
-									word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+										v = activation_forward_call(activation, v);
+									word |= (static_cast<uint32_t>(float_to_int8_rn_sat(v)) & 0xFFu) << (8 * b);
 								}
 								packed[w] = word;
 							}
@@ -411,8 +414,8 @@ namespace
 								}
 								else if (activation != AVOCADO_ACTIVATION_LINEAR)
 								{
-									v0 = activation_forward(activation, v0);
-									v1 = activation_forward(activation, v1);
+									v0 = activation_forward_call(activation, v0);
+									v1 = activation_forward_call(activation, v1);
 								}
 								if (p.beta != 0.0f)
 								{
@@ -565,6 +568,11 @@ namespace
 
 namespace bk
 {
+	__device__ __noinline__ float activation_forward_call(avocado::backend::avActivationType_t activation, float x)
+	{
+		return activation_forward(activation, x);
+	}
+
 	avStatus_t launch_implicit_gemm_tc(ContextObject &ctx, const ConvArgs &args, avDataType_t xType, avDataType_t yType, const void *alpha1,
 			const void *alpha2, const void *beta)
 	{

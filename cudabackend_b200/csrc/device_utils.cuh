@@ -81,6 +81,25 @@ namespace bk
 		*reinterpret_cast<Vec<T, N>*>(ptr) = value;
 	}
 
+	/* Integer <-> float conversions built from FP32 adds and one FMA.  The hardware conversion instructions have a
+	 * small fraction of the FP32 rate, and the requantisation epilogues convert every output element twice.
+	 * Both functions round to nearest even, exactly like cvt.rn.f32.s32 and cvt.rni.sat.s8.f32.
+	 * 12582912 = 1.5 * 2^23: adding it to an integer |i| < 2^22 places i in the low mantissa bits. */
+	__device__ __forceinline__ float small_int_to_float(int32_t i) /* exact for |i| < 2^22 */
+	{
+		return __int_as_float(0x4B400000 + i) - 12582912.0f;
+	}
+	__device__ __forceinline__ float int_to_float_rn(int32_t t)
+	{
+		/* t = hi * 4096 + lo with both parts exact in float; the FMA rounds the exact sum once */
+		return fmaf(small_int_to_float(t >> 12), 4096.0f, small_int_to_float(t & 0xFFF));
+	}
+	__device__ __forceinline__ int32_t float_to_int8_rn_sat(float v) /* NaN gives -128 */
+	{
+		v = fminf(fmaxf(v, -128.0f), 127.0f);
+		return __float_as_int(v + 12582912.0f) - 0x4B400000;
+	}
+
 	template<typename CT>
 	__device__ __forceinline__ CT activation_forward(avocado::backend::avActivationType_t activation, CT x)
 	{
@@ -109,6 +128,9 @@ namespace bk
 				return x / (fabs(x) + static_cast<CT>(1));
 		}
 	}
+	/* The same switch behind a call, for epilogues that are unrolled many times: inlining the transcendental cases into
+	 * every copy makes the loop body larger than the instruction cache even when only linear / relu ever run. */
+	__device__ __noinline__ float activation_forward_call(avocado::backend::avActivationType_t activation, float x);
 } /* namespace bk */
 
 #endif /* B200_DEVICE_UTILS_CUH_ */

@@ -293,7 +293,7 @@ void oracle_conv2d_forward_int8(const int8_t *x, const int8_t *w, const int32_t 
 						r = activate_f32(activation, r);
 						float q = nearbyintf(r);
 						if (q != q)
-							q = 0.0f; /* NaN converts to 0, as the GPU's saturating convert does */
+							q = -128.0f; /* NaN saturates to -128, the library's convention */
 						if (q < -128.0f)
 							q = -128.0f;
 						if (q > 127.0f)
