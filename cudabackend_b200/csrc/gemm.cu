@@ -23,6 +23,7 @@
 #include "objects.hpp"
 #include "device_utils.cuh"
 #include "umma.cuh"
+#include "winograd_internal.hpp"
 
 #include <cstdlib>
 #include <cstring>
@@ -597,6 +598,39 @@ namespace
 	}
 }
 
+namespace bk
+{
+	avStatus_t gemm_batched(ContextObject &ctx, bool transA, bool transB, const void *alpha, const TensorObject &a, const void *aPtr, const TensorObject &b,
+			const void *bPtr, const void *beta, const TensorObject &c, void *cPtr)
+	{
+		if (a.nb_dims != 3 or b.nb_dims != 3 or c.nb_dims != 3)
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (a.dtype != b.dtype)
+			return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		/* the int8 case exists only in the non-batched call of the reference (src/gemm.cpp:146-208) */
+		if (c.dtype == AVOCADO_DTYPE_INT32 or c.dtype == AVOCADO_DTYPE_INT8)
+			return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		GemmShape s;
+		s.batch = a.dims[0];
+		s.transA = transA;
+		s.transB = transB;
+		s.M = s.transA ? a.dims[2] : a.dims[1];
+		s.Kc = s.transA ? a.dims[1] : a.dims[2];
+		s.N = s.transB ? b.dims[1] : b.dims[2];
+		const int kb = s.transB ? b.dims[2] : b.dims[1];
+		if (b.dims[0] != s.batch or c.dims[0] != s.batch or kb != s.Kc or c.dims[1] != s.M or c.dims[2] != s.N)
+			return AVOCADO_STATUS_BAD_PARAM;
+		s.lda = a.dims[2];
+		s.ldb = b.dims[2];
+		s.ldc = c.dims[2];
+		s.strideA = a.volumeWithoutFirstDim();
+		s.strideB = b.volumeWithoutFirstDim();
+		s.strideC = c.volumeWithoutFirstDim();
+		ctx.setDevice();
+		return gemm_dispatch(ctx, s, a.dtype, c.dtype, alpha, beta, aPtr, bPtr, cPtr);
+	}
+} /* namespace bk */
+
 namespace avocado
 {
 	namespace backend
@@ -642,35 +676,8 @@ namespace avocado
 				const void *beta, const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem)
 		{
 			AVOCADO_API_BEGIN
-				ContextObject &ctx = getContext(context);
-				const TensorObject &a = getTensor(aDesc);
-				const TensorObject &b = getTensor(bDesc);
-				const TensorObject &c = getTensor(cDesc);
-				if (a.nb_dims != 3 or b.nb_dims != 3 or c.nb_dims != 3)
-					return AVOCADO_STATUS_BAD_PARAM;
-				if (a.dtype != b.dtype)
-					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				/* the int8 case exists only in the non-batched call of the reference (src/gemm.cpp:146-208) */
-				if (c.dtype == AVOCADO_DTYPE_INT32 or c.dtype == AVOCADO_DTYPE_INT8)
-					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				GemmShape s;
-				s.batch = a.dims[0];
-				s.transA = is_transpose(aOp);
-				s.transB = is_transpose(bOp);
-				s.M = s.transA ? a.dims[2] : a.dims[1];
-				s.Kc = s.transA ? a.dims[1] : a.dims[2];
-				s.N = s.transB ? b.dims[1] : b.dims[2];
-				const int kb = s.transB ? b.dims[2] : b.dims[1];
-				if (b.dims[0] != s.batch or c.dims[0] != s.batch or kb != s.Kc or c.dims[1] != s.M or c.dims[2] != s.N)
-					return AVOCADO_STATUS_BAD_PARAM;
-				s.lda = a.dims[2];
-				s.ldb = b.dims[2];
-				s.ldc = c.dims[2];
-				s.strideA = a.volumeWithoutFirstDim();
-				s.strideB = b.volumeWithoutFirstDim();
-				s.strideC = c.volumeWithoutFirstDim();
-				ctx.setDevice();
-				return gemm_dispatch(ctx, s, a.dtype, c.dtype, alpha, beta, getPointer(aMem), getPointer(bMem), getPointer(cMem));
+				return bk::gemm_batched(getContext(context), is_transpose(aOp), is_transpose(bOp), alpha, getTensor(aDesc), getPointer(aMem), getTensor(bDesc),
+						getPointer(bMem), beta, getTensor(cDesc), getPointer(cMem));
 			AVOCADO_API_END
 		}
 	} /* namespace backend */

@@ -1,0 +1,31 @@
+/*
+ * winograd_internal.hpp -- the transform and contraction launchers behind the C entry points, callable with objects
+ * and raw device pointers instead of handles.  The one-call fused convolution chains them on the context's scratch
+ * buffer; the entry points of winograd_nonfused.cu and gemm.cu are thin wrappers over the same functions.
+ */
+#ifndef B200_WINOGRAD_INTERNAL_HPP_
+#define B200_WINOGRAD_INTERNAL_HPP_
+
+#include "objects.hpp"
+
+namespace bk
+{
+	avocado::backend::avStatus_t winograd_weight_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
+			int transformSize, const avocado::backend::b200::TensorObject &w, const void *wPtr, const avocado::backend::b200::TensorObject &m, void *mPtr);
+
+	avocado::backend::avStatus_t winograd_input_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
+			int transformSize, const avocado::backend::b200::TensorObject &w, const avocado::backend::b200::TensorObject &x, const void *xPtr,
+			const avocado::backend::b200::TensorObject &m, void *mPtr);
+
+	avocado::backend::avStatus_t winograd_output_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
+			int transformSize, const avocado::backend::b200::TensorObject &w, const void *alpha1, const avocado::backend::b200::TensorObject &m,
+			const void *mPtr, const avocado::backend::b200::TensorObject &y, void *yPtr, const void *bPtr, const void *alpha2, const void *zPtr,
+			const void *beta, avocado::backend::avActivationType_t activation);
+
+	/* C[i] = alpha * op(A[i]) * op(B[i]) + beta * C[i] on row-major 3-D tensors */
+	avocado::backend::avStatus_t gemm_batched(avocado::backend::b200::ContextObject &ctx, bool transA, bool transB, const void *alpha,
+			const avocado::backend::b200::TensorObject &a, const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const void *beta,
+			const avocado::backend::b200::TensorObject &c, void *cPtr);
+} /* namespace bk */
+
+#endif /* B200_WINOGRAD_INTERNAL_HPP_ */

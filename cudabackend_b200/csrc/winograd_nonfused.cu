@@ -20,6 +20,7 @@
 #include "device_utils.cuh"
 #include "winograd_tables.cuh"
 #include "winograd_f43.cuh"
+#include "winograd_internal.hpp"
 
 #include <cuda_runtime_api.h>
 
@@ -694,10 +695,11 @@ namespace
 		return checkForErrors();
 	}
 
-	/* which (tensor dtype, matrices dtype) pairs exist: equal types, or 16-bit tensors with float32 matrices */
+	/* which (tensor dtype, matrices dtype) pairs exist: equal types, 16-bit tensors with float32 matrices, and bfloat16
+	 * tensors with float16 matrices (the 10-bit mantissa keeps F(2x2,3x3) inside 1e-2 where a bfloat16 domain does not) */
 	enum class Pairing
 	{
-		F16_F16, F16_F32, BF16_BF16, BF16_F32, F32_F32, F64_F64, Unsupported
+		F16_F16, F16_F32, BF16_BF16, BF16_F16, BF16_F32, F32_F32, F64_F64, Unsupported
 	};
 	Pairing classify(avDataType_t tensorType, avDataType_t matrixType)
 	{
@@ -706,7 +708,8 @@ namespace
 			case AVOCADO_DTYPE_FLOAT16:
 				return matrixType == AVOCADO_DTYPE_FLOAT16 ? Pairing::F16_F16 : matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::F16_F32 : Pairing::Unsupported;
 			case AVOCADO_DTYPE_BFLOAT16:
-				return matrixType == AVOCADO_DTYPE_BFLOAT16 ? Pairing::BF16_BF16 : matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::BF16_F32 : Pairing::Unsupported;
+				return matrixType == AVOCADO_DTYPE_BFLOAT16 ? Pairing::BF16_BF16 : matrixType == AVOCADO_DTYPE_FLOAT16 ? Pairing::BF16_F16 :
+						matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::BF16_F32 : Pairing::Unsupported;
 			case AVOCADO_DTYPE_FLOAT32:
 				return matrixType == AVOCADO_DTYPE_FLOAT32 ? Pairing::F32_F32 : Pairing::Unsupported;
 			case AVOCADO_DTYPE_FLOAT64:
@@ -716,6 +719,111 @@ namespace
 		}
 	}
 }
+
+namespace bk
+{
+	using namespace avocado::backend;
+	using namespace avocado::backend::b200;
+
+	avStatus_t winograd_weight_transform(ContextObject &ctx, const ConvolutionObject &conv, int transformSize, const TensorObject &w, const void *wPtr, const TensorObject &m, void *mPtr)
+	{
+		if (not tile_config_supported(w, transformSize))
+			return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+		if (wPtr == nullptr or mPtr == nullptr)
+			return AVOCADO_STATUS_BAD_PARAM;
+		ctx.setDevice();
+		switch (classify(w.dtype, m.dtype))
+		{
+			case Pairing::F16_F16:
+				return launch_weight_transform<half, half>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			case Pairing::F16_F32:
+				return launch_weight_transform<half, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			case Pairing::BF16_BF16:
+				return launch_weight_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			case Pairing::BF16_F16:
+				return launch_weight_transform<__nv_bfloat16, half>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			case Pairing::BF16_F32:
+				return launch_weight_transform<__nv_bfloat16, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			case Pairing::F32_F32:
+				return launch_weight_transform<float, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			case Pairing::F64_F64:
+				return launch_weight_transform<double, double>(ctx, conv, w, wPtr, m, mPtr, transformSize);
+			default:
+				return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		}
+	}
+
+	avStatus_t winograd_input_transform(ContextObject &ctx, const ConvolutionObject &conv, int transformSize, const TensorObject &w, const TensorObject &x, const void *xPtr,
+			const TensorObject &m, void *mPtr)
+	{
+		if (not tile_config_supported(w, transformSize))
+			return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+		if (xPtr == nullptr or mPtr == nullptr)
+			return AVOCADO_STATUS_BAD_PARAM;
+		ctx.setDevice();
+		/* the reference switches on the dtype of w (src/winograd_nonfused.cu:914); x must agree with it */
+		if (x.dtype != w.dtype)
+			return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		switch (classify(w.dtype, m.dtype))
+		{
+			case Pairing::F16_F16:
+				return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			case Pairing::F16_F32:
+				return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			case Pairing::BF16_BF16:
+				return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			case Pairing::BF16_F16:
+				return launch_input_transform<__nv_bfloat16, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			case Pairing::BF16_F32:
+				return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			case Pairing::F32_F32:
+				return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			case Pairing::F64_F64:
+				return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+			default:
+				return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		}
+	}
+
+	avStatus_t winograd_output_transform(ContextObject &ctx, const ConvolutionObject &conv, int transformSize, const TensorObject &w, const void *alpha1, const TensorObject &m,
+			const void *mPtr, const TensorObject &y, void *yPtr, const void *bPtr, const void *alpha2, const void *zPtr, const void *beta,
+			avActivationType_t activation)
+	{
+		if (not tile_config_supported(w, transformSize))
+			return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
+		if (yPtr == nullptr or mPtr == nullptr)
+			return AVOCADO_STATUS_BAD_PARAM;
+		if (y.dtype != w.dtype)
+			return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		ctx.setDevice();
+		switch (classify(w.dtype, m.dtype))
+		{
+			case Pairing::F16_F16:
+				return launch_output_transform<half, half, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+						transformSize);
+			case Pairing::F16_F32:
+				return launch_output_transform<half, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+						transformSize);
+			case Pairing::BF16_BF16:
+				return launch_output_transform<__nv_bfloat16, __nv_bfloat16, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta,
+						activation, transformSize);
+			case Pairing::BF16_F16:
+				return launch_output_transform<__nv_bfloat16, half, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+						transformSize);
+			case Pairing::BF16_F32:
+				return launch_output_transform<__nv_bfloat16, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+						transformSize);
+			case Pairing::F32_F32:
+				return launch_output_transform<float, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+						transformSize);
+			case Pairing::F64_F64:
+				return launch_output_transform<double, double, double>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
+						transformSize);
+			default:
+				return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		}
+	}
+} /* namespace bk */
 
 namespace avocado
 {
@@ -727,32 +835,7 @@ namespace avocado
 			AVOCADO_API_BEGIN
 				ContextObject &ctx = getContext(context);
 				const ConvolutionObject &conv = getConvolution(config);
-				const TensorObject &w = getTensor(wDesc);
-				const TensorObject &m = getTensor(matricesDesc);
-				const void *wPtr = getPointer(wMem);
-				void *mPtr = getPointer(matricesMem);
-				if (not tile_config_supported(w, transformSize))
-					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
-				if (wPtr == nullptr or mPtr == nullptr)
-					return AVOCADO_STATUS_BAD_PARAM;
-				ctx.setDevice();
-				switch (classify(w.dtype, m.dtype))
-				{
-					case Pairing::F16_F16:
-						return launch_weight_transform<half, half>(ctx, conv, w, wPtr, m, mPtr, transformSize);
-					case Pairing::F16_F32:
-						return launch_weight_transform<half, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
-					case Pairing::BF16_BF16:
-						return launch_weight_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, wPtr, m, mPtr, transformSize);
-					case Pairing::BF16_F32:
-						return launch_weight_transform<__nv_bfloat16, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
-					case Pairing::F32_F32:
-						return launch_weight_transform<float, float>(ctx, conv, w, wPtr, m, mPtr, transformSize);
-					case Pairing::F64_F64:
-						return launch_weight_transform<double, double>(ctx, conv, w, wPtr, m, mPtr, transformSize);
-					default:
-						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				}
+				return bk::winograd_weight_transform(ctx, conv, transformSize, getTensor(wDesc), getPointer(wMem), getTensor(matricesDesc), getPointer(matricesMem));
 			AVOCADO_API_END
 		}
 
@@ -763,36 +846,7 @@ namespace avocado
 			AVOCADO_API_BEGIN
 				ContextObject &ctx = getContext(context);
 				const ConvolutionObject &conv = getConvolution(config);
-				const TensorObject &w = getTensor(wDesc);
-				const TensorObject &x = getTensor(xDesc);
-				const TensorObject &m = getTensor(matricesDesc);
-				const void *xPtr = getPointer(xMem);
-				void *mPtr = getPointer(matricesMem);
-				if (not tile_config_supported(w, transformSize))
-					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
-				if (xPtr == nullptr or mPtr == nullptr)
-					return AVOCADO_STATUS_BAD_PARAM;
-				ctx.setDevice();
-				/* the reference switches on the dtype of w (src/winograd_nonfused.cu:914); x must agree with it */
-				if (x.dtype != w.dtype)
-					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				switch (classify(w.dtype, m.dtype))
-				{
-					case Pairing::F16_F16:
-						return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
-					case Pairing::F16_F32:
-						return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
-					case Pairing::BF16_BF16:
-						return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
-					case Pairing::BF16_F32:
-						return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
-					case Pairing::F32_F32:
-						return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
-					case Pairing::F64_F64:
-						return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
-					default:
-						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				}
+				return bk::winograd_input_transform(ctx, conv, transformSize, getTensor(wDesc), getTensor(xDesc), getPointer(xMem), getTensor(matricesDesc), getPointer(matricesMem));
 			AVOCADO_API_END
 		}
 
@@ -804,45 +858,10 @@ namespace avocado
 			AVOCADO_API_BEGIN
 				ContextObject &ctx = getContext(context);
 				const ConvolutionObject &conv = getConvolution(config);
-				const TensorObject &w = getTensor(wDesc);
-				const TensorObject &m = getTensor(matricesDesc);
-				const TensorObject &y = getTensor(yDesc);
-				const void *mPtr = getPointer(matricesMem);
-				void *yPtr = getPointer(yMem);
-				const void *bPtr = getPointer(bMem);
-				const void *zPtr = getPointer(zMem);
 				(void) bDesc;
 				(void) zDesc;
-				if (not tile_config_supported(w, transformSize))
-					return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
-				if (yPtr == nullptr or mPtr == nullptr)
-					return AVOCADO_STATUS_BAD_PARAM;
-				if (y.dtype != w.dtype)
-					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				ctx.setDevice();
-				switch (classify(w.dtype, m.dtype))
-				{
-					case Pairing::F16_F16:
-						return launch_output_transform<half, half, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
-								transformSize);
-					case Pairing::F16_F32:
-						return launch_output_transform<half, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
-								transformSize);
-					case Pairing::BF16_BF16:
-						return launch_output_transform<__nv_bfloat16, __nv_bfloat16, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta,
-								activation, transformSize);
-					case Pairing::BF16_F32:
-						return launch_output_transform<__nv_bfloat16, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
-								transformSize);
-					case Pairing::F32_F32:
-						return launch_output_transform<float, float, float>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
-								transformSize);
-					case Pairing::F64_F64:
-						return launch_output_transform<double, double, double>(ctx, conv, w, alpha1, m, mPtr, y, yPtr, bPtr, alpha2, zPtr, beta, activation,
-								transformSize);
-					default:
-						return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				}
+				return bk::winograd_output_transform(ctx, conv, transformSize, getTensor(wDesc), alpha1, getTensor(matricesDesc), getPointer(matricesMem), getTensor(yDesc), getPointer(yMem),
+						getPointer(bMem), alpha2, getPointer(zMem), beta, activation);
 			AVOCADO_API_END
 		}
 
