@@ -21,6 +21,7 @@ ACTIVATIONS = {"linear": 0, "sigmoid": 1, "tanh": 2, "relu": 3, "selu": 4, "elu"
 CONVOLUTION_MODE, CROSS_CORRELATION_MODE = 0, 1
 GEMM_N, GEMM_T = 0, 1
 INVALID = -1
+NO_ALLOC_SCRATCH_BYTES = 8 * 1024 * 1024  # AVOCADO_NO_ALLOC_SCRATCH_BYTES
 
 _H = ctypes.c_int64  # every descriptor handle
 _I64 = ctypes.c_int64
@@ -79,6 +80,7 @@ SIGNATURES = {
     "cudaContextEndCapture": (_INT, [_H, ctypes.POINTER(_I64)]),
     "cudaContextLaunchGraph": (_INT, [_H, _I64]),
     "cudaDestroyCapturedGraph": (_INT, [_I64]),
+    "cudaConvolutionWinogradFusedForwardNoAlloc": (_INT, _conv_args),
 }
 
 # exported for link compatibility, return NOT_SUPPORTED

@@ -441,7 +441,7 @@ namespace
 
 	template<int BLOCK_N, int STAGES, int EPI_BUFS, bool IS_BF16>
 	avStatus_t launch_tc_config(ContextObject &ctx, const GemmShape &s, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC,
-			float alpha)
+			float alpha, int *deviceStatus)
 	{
 		using Cfg = TcConfig<BLOCK_N, STAGES, EPI_BUFS>;
 		auto kernel = kernel_gemm_nt_tc<BLOCK_N, STAGES, EPI_BUFS, IS_BF16>;
@@ -463,7 +463,7 @@ namespace
 		const int ctasPerSm = (Cfg::kSmemBytes <= 110 * 1024 and Cfg::kTmemColumns <= 256) ? 2 : 1;
 		const int grid = static_cast<int>(std::min<long long>(tiles, static_cast<long long>(sms) * ctasPerSm));
 		kernel<<<grid, kTcThreads, Cfg::kSmemBytes, ctx.getStream()>>>(mapA, mapB, mapC, mBlocks, nBlocks, kBlocks, static_cast<int>(tiles), s.N, alpha,
-				ctx.getDeviceStatus());
+				deviceStatus);
 		return checkForErrors();
 	}
 
@@ -505,7 +505,7 @@ namespace
 		return true;
 	}
 
-	avStatus_t launch_tc(ContextObject &ctx, const GemmShape &s, avDataType_t dtype, const void *A, const void *B, void *C, float alpha)
+	avStatus_t launch_tc(ContextObject &ctx, const GemmShape &s, avDataType_t dtype, const void *A, const void *B, void *C, float alpha, int *deviceStatus)
 	{
 		const CUtensorMapDataType type = (dtype == AVOCADO_DTYPE_BFLOAT16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 		const int blockN = (s.N <= 64) ? 64 : (s.N <= 128) ? 128 : 256;
@@ -535,11 +535,11 @@ namespace
 		switch (blockN)
 		{
 			case 64:
-				return bf16 ? launch_tc_config<64, 3, 2, true>(ctx, s, mapA, mapB, mapC, alpha) : launch_tc_config<64, 3, 2, false>(ctx, s, mapA, mapB, mapC, alpha);
+				return bf16 ? launch_tc_config<64, 3, 2, true>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus) : launch_tc_config<64, 3, 2, false>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus);
 			case 128:
-				return bf16 ? launch_tc_config<128, 3, 2, true>(ctx, s, mapA, mapB, mapC, alpha) : launch_tc_config<128, 3, 2, false>(ctx, s, mapA, mapB, mapC, alpha);
+				return bf16 ? launch_tc_config<128, 3, 2, true>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus) : launch_tc_config<128, 3, 2, false>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus);
 			default:
-				return bf16 ? launch_tc_config<256, 2, 1, true>(ctx, s, mapA, mapB, mapC, alpha) : launch_tc_config<256, 2, 1, false>(ctx, s, mapA, mapB, mapC, alpha);
+				return bf16 ? launch_tc_config<256, 2, 1, true>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus) : launch_tc_config<256, 2, 1, false>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus);
 		}
 	}
 
@@ -575,7 +575,7 @@ namespace
 				if (forced_path() == 2 and not eligible)
 					return AVOCADO_STATUS_NOT_SUPPORTED;
 				if (eligible and forced_path() != 1)
-					return launch_tc(ctx, s, cType, A, B, C, a);
+					return launch_tc(ctx, s, cType, A, B, C, a, ctx.getDeviceStatus());
 				if (cType == AVOCADO_DTYPE_FLOAT16)
 					return launch_simt<half, float, half>(stream, s, A, B, C, a, b);
 				return launch_simt<__nv_bfloat16, float, __nv_bfloat16>(stream, s, A, B, C, a, b);
@@ -628,6 +628,32 @@ namespace bk
 		s.strideC = c.volumeWithoutFirstDim();
 		ctx.setDevice();
 		return gemm_dispatch(ctx, s, a.dtype, c.dtype, alpha, beta, aPtr, bPtr, cPtr);
+	}
+
+	avStatus_t gemm_batched_nt_tensor_core(ContextObject &ctx, const TensorObject &a, const void *aPtr, const TensorObject &b, const void *bPtr,
+			const TensorObject &c, void *cPtr, int *deviceStatus)
+	{
+		if (a.nb_dims != 3 or b.nb_dims != 3 or c.nb_dims != 3 or a.dtype != b.dtype or a.dtype != c.dtype)
+			return AVOCADO_STATUS_BAD_PARAM;
+		GemmShape s;
+		s.batch = a.dims[0];
+		s.transA = false;
+		s.transB = true;
+		s.M = a.dims[1];
+		s.Kc = a.dims[2];
+		s.N = b.dims[1];
+		if (b.dims[0] != s.batch or c.dims[0] != s.batch or b.dims[2] != s.Kc or c.dims[1] != s.M or c.dims[2] != s.N)
+			return AVOCADO_STATUS_BAD_PARAM;
+		s.lda = s.Kc;
+		s.ldb = s.Kc;
+		s.ldc = s.N;
+		s.strideA = a.volumeWithoutFirstDim();
+		s.strideB = b.volumeWithoutFirstDim();
+		s.strideC = c.volumeWithoutFirstDim();
+		if (not tc_eligible(ctx, s, c.dtype, aPtr, bPtr, cPtr, 0.0f))
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		ctx.setDevice();
+		return launch_tc(ctx, s, c.dtype, aPtr, bPtr, cPtr, 1.0f, deviceStatus);
 	}
 } /* namespace bk */
 

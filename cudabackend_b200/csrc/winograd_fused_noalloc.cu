@@ -1,0 +1,163 @@
+/*
+ * winograd_fused_noalloc.cu -- cudaConvolutionWinogradFusedForwardNoAlloc: the one-call Winograd convolution for
+ * callers that must not trigger a device allocation.
+ *
+ * Who needs this.  cudaConvolutionWinogradFusedForward keeps its transform-domain tensors in a scratch buffer that
+ * the context allocates with cudaMalloc the first time (and every time a larger layer arrives).  Some hosts cannot
+ * tolerate that: an inference server that has handed the whole GPU to its own memory pool has nothing left for
+ * cudaMalloc to return; a latency-bound control loop cannot absorb the device-wide synchronisation an allocation
+ * implies; a process running under a "no allocation after start-up" policy is simply not allowed to.  For them the
+ * scratch lives in the library image itself: a file-scope __device__ array, reserved on every GPU that loads the
+ * library for as long as the process lives, and limited to AVOCADO_NO_ALLOC_SCRATCH_BYTES.
+ *
+ * What it computes: exactly what cudaConvolutionWinogradFusedForward computes for float16 and bfloat16 tensors with a
+ * 3x3 kernel (same kernels, same order, bit-identical result), as long as the three transform-domain tensors fit:
+ *     16 * 2 bytes * (K*C + tiles*C + tiles*K) <= AVOCADO_NO_ALLOC_SCRATCH_BYTES,   tiles = N * ceil(H/2) * ceil(W/2)
+ * A larger problem is refused with AVOCADO_STATUS_BAD_PARAM before anything is launched.
+ *
+ * Rules for the caller:
+ *  - The first call on each device looks up the device address of the array (cudaGetSymbolAddress with that device
+ *    current) and sets the kernels' shared-memory attributes.  Make that first call before any stream capture.
+ *  - All calls on a device share the one array, whatever context they use.  Two calls whose work overlaps on the
+ *    GPU (different streams, no ordering between them) race on it; order them or use the allocating entry point.
+ *  - The array keeps the previous call's contents.  Nothing needs to start from zero except the 256-byte word in
+ *    which the tensor-core kernel reports a wait that ran out; each call clears it on its stream first.
+ *  - No cudaMalloc, cudaFree or allocating library routine is called on this path.
+ */
+#include <Avocado/cuda_backend.h>
+#include <Avocado/cuda_backend_ext.h>
+
+#include "objects.hpp"
+#include "winograd_internal.hpp"
+
+#include <mutex>
+
+namespace
+{
+	using namespace avocado::backend;
+	using namespace avocado::backend::b200;
+
+	constexpr size_t kStatusBytes = 256;
+	constexpr size_t kScratchBytes = AVOCADO_NO_ALLOC_SCRATCH_BYTES;
+
+	/* [0, 256): error word of the tensor-core kernel; [256, 256 + kScratchBytes): U, V and M.
+	 * In host code this name is only a stand-in for the symbol, never a device address. */
+	static __device__ __align__(256) unsigned char no_alloc_scratch[kStatusBytes + kScratchBytes];
+
+	/* device address of the array, looked up once per device with that device current */
+	avStatus_t scratch_address(int device, unsigned char **result)
+	{
+		static std::mutex mutex;
+		static unsigned char *address[kMaxDevices] = { };
+		if (device < 0 or device >= kMaxDevices)
+			return AVOCADO_STATUS_BAD_PARAM;
+		std::lock_guard<std::mutex> lock(mutex);
+		if (address[device] == nullptr)
+		{
+			if (cudaSetDevice(device) != cudaSuccess)
+				return AVOCADO_STATUS_EXECUTION_FAILED;
+			unsigned char *ptr = nullptr;
+			const cudaError_t status = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), no_alloc_scratch);
+			if (status != cudaSuccess or ptr == nullptr)
+			{
+				cudaGetLastError();
+				return AVOCADO_STATUS_EXECUTION_FAILED;
+			}
+			address[device] = ptr;
+		}
+		result[0] = address[device];
+		return AVOCADO_STATUS_SUCCESS;
+	}
+
+	size_t align_up(size_t value, size_t alignment)
+	{
+		return (value + alignment - 1) / alignment * alignment;
+	}
+	TensorObject make_tensor(avDataType_t dtype, std::initializer_list<int> dims)
+	{
+		TensorObject t;
+		t.dtype = dtype;
+		t.nb_dims = static_cast<int>(dims.size());
+		int i = 0;
+		for (int d : dims)
+			t.dims[i++] = d;
+		return t;
+	}
+}
+
+namespace avocado
+{
+	namespace backend
+	{
+		avStatus_t cudaConvolutionWinogradFusedForwardNoAlloc(avContextDescriptor_t context, const avConvolutionDescriptor_t config, const void *alpha1,
+				const avTensorDescriptor_t xDesc, const avMemoryDescriptor_t xMem, const avTensorDescriptor_t wDesc, const avMemoryDescriptor_t wMem,
+				const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem, const void *alpha2, const avTensorDescriptor_t zDesc,
+				const avMemoryDescriptor_t zMem, const void *beta, const avTensorDescriptor_t yDesc, avMemoryDescriptor_t yMem, avActivationType_t activation)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				const ConvolutionObject &conv = getConvolution(config);
+				const TensorObject &x = getTensor(xDesc);
+				const TensorObject &w = getTensor(wDesc);
+				const TensorObject &y = getTensor(yDesc);
+				const void *xPtr = getPointer(xMem);
+				const void *wPtr = getPointer(wMem);
+				void *yPtr = getPointer(yMem);
+				const void *bPtr = getPointer(bMem);
+				const void *zPtr = getPointer(zMem);
+				if (x.nb_dims != 4 or w.nb_dims != 4 or y.nb_dims != 4 or xPtr == nullptr or wPtr == nullptr or yPtr == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM;
+				if (x.dims[3] != w.dims[3] or y.dims[3] != w.dims[0] or y.dims[0] != x.dims[0] or y.dims[1] != x.dims[1] or y.dims[2] != x.dims[2])
+					return AVOCADO_STATUS_BAD_PARAM;
+				if (x.dtype != AVOCADO_DTYPE_FLOAT16 and x.dtype != AVOCADO_DTYPE_BFLOAT16)
+					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				if (w.dtype != x.dtype or y.dtype != x.dtype or (zPtr != nullptr and getTensor(zDesc).dtype != x.dtype)
+						or (bPtr != nullptr and getTensor(bDesc).dtype != AVOCADO_DTYPE_FLOAT32))
+					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+				if (w.dims[1] != 3 or w.dims[2] != 3 or conv.strides[0] != 1 or conv.strides[1] != 1 or conv.dilation[0] != 1 or conv.dilation[1] != 1
+						or conv.groups != 1 or not conv.paddingValueIsZero())
+					return AVOCADO_STATUS_NOT_SUPPORTED;
+
+				const int batch = x.dims[0], height = x.dims[1], width = x.dims[2], channels = x.dims[3], filters = w.dims[0];
+				const long long tiles = static_cast<long long>(batch) * ((height + 1) / 2) * ((width + 1) / 2);
+				if (tiles == 0 or channels == 0 or filters == 0)
+					return AVOCADO_STATUS_SUCCESS;
+				constexpr int planes = 16;
+				const size_t u_bytes = align_up(static_cast<size_t>(planes) * filters * channels * 2, 256);
+				const size_t v_bytes = align_up(static_cast<size_t>(planes) * tiles * channels * 2, 256);
+				const size_t m_bytes = align_up(static_cast<size_t>(planes) * tiles * filters * 2, 256);
+				/* the fixed array is all there is: a problem that does not fit is refused, never trimmed */
+				if (tiles > 0x7FFFFFFFll or u_bytes + v_bytes + m_bytes > kScratchBytes)
+					return AVOCADO_STATUS_BAD_PARAM;
+
+				unsigned char *base = nullptr;
+				const avStatus_t lookup = scratch_address(ctx.device, &base);
+				if (lookup != AVOCADO_STATUS_SUCCESS)
+					return lookup;
+				ctx.setDevice();
+				int *status_word = reinterpret_cast<int*>(base);
+				void *u_ptr = base + kStatusBytes;
+				void *v_ptr = base + kStatusBytes + u_bytes;
+				void *m_ptr = base + kStatusBytes + u_bytes + v_bytes;
+				if (cudaMemsetAsync(status_word, 0, kStatusBytes, ctx.getStream()) != cudaSuccess)
+					return checkForErrors();
+
+				const avDataType_t domain = AVOCADO_DTYPE_FLOAT16;
+				const TensorObject u = make_tensor(domain, { planes, filters, channels });
+				const TensorObject v = make_tensor(domain, { planes, static_cast<int>(tiles), channels });
+				const TensorObject m = make_tensor(domain, { planes, static_cast<int>(tiles), filters });
+
+				avStatus_t status = bk::winograd_weight_transform(ctx, conv, 2, w, wPtr, u, u_ptr);
+				if (status != AVOCADO_STATUS_SUCCESS)
+					return status;
+				status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr);
+				if (status != AVOCADO_STATUS_SUCCESS)
+					return status;
+				status = bk::gemm_batched_nt_tensor_core(ctx, v, v_ptr, u, u_ptr, m, m_ptr, status_word);
+				if (status != AVOCADO_STATUS_SUCCESS)
+					return status;
+				return bk::winograd_output_transform(ctx, conv, 2, w, alpha1, m, m_ptr, y, yPtr, bPtr, alpha2, zPtr, beta, activation);
+			AVOCADO_API_END
+		}
+	} /* namespace backend */
+} /* namespace avocado */

@@ -26,6 +26,12 @@ namespace bk
 	avocado::backend::avStatus_t gemm_batched(avocado::backend::b200::ContextObject &ctx, bool transA, bool transB, const void *alpha,
 			const avocado::backend::b200::TensorObject &a, const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const void *beta,
 			const avocado::backend::b200::TensorObject &c, void *cPtr);
+
+	/* C[i] = A[i] * B[i]^T on the tensor-core kernel only, with the kernel's error word at a caller-chosen address;
+	 * returns NOT_SUPPORTED instead of falling back when the shape is outside what that kernel covers */
+	avocado::backend::avStatus_t gemm_batched_nt_tensor_core(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::TensorObject &a,
+			const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const avocado::backend::b200::TensorObject &c, void *cPtr,
+			int *deviceStatus);
 } /* namespace bk */
 
 #endif /* B200_WINOGRAD_INTERNAL_HPP_ */

@@ -182,5 +182,9 @@ class DirectConvolution:
     def winograd_fused(self, alpha1=None, alpha2=None, beta=None, activation="linear"):
         self._run("cudaConvolutionWinogradFusedForward", alpha1, alpha2, beta, activation)
 
+    def winograd_fused_no_alloc(self, alpha1=None, alpha2=None, beta=None, activation="linear"):
+        """Same convolution through the entry point that keeps its scratch in a fixed array inside the library."""
+        self._run("cudaConvolutionWinogradFusedForwardNoAlloc", alpha1, alpha2, beta, activation)
+
     def implicit_gemm(self, alpha1=None, alpha2=None, beta=None, activation="linear"):
         self._run("cudaConvolutionImplicitGemmForward", alpha1, alpha2, beta, activation)

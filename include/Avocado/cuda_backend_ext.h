@@ -49,6 +49,28 @@ DLL_PUBLIC avStatus_t cudaContextEndCapture(avContextDescriptor_t context, av_in
 DLL_PUBLIC avStatus_t cudaContextLaunchGraph(avContextDescriptor_t context, av_int64 graph);
 DLL_PUBLIC avStatus_t cudaDestroyCapturedGraph(av_int64 graph);
 
+/* Size of the fixed scratch array behind cudaConvolutionWinogradFusedForwardNoAlloc.  Every GPU that loads the
+ * library reserves this much device memory (plus 256 bytes) from load until the process exits. */
+#define AVOCADO_NO_ALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
+
+/* cudaConvolutionWinogradFusedForward for callers that may not cause a device allocation -- a host that has given
+ * all GPU memory to its own pool, a latency-bound loop that cannot absorb the synchronisation cudaMalloc implies, a
+ * process under a no-allocation-after-start-up rule.  Same arguments and same result, but the transform-domain
+ * tensors live in a fixed array inside the library image instead of the context's cudaMalloc'ed scratch, and nothing
+ * on this path allocates or frees.  It has no counterpart in the reference (whose fused entry point takes no
+ * workspace and allocates none because it was never finished).
+ *  - float16 / bfloat16 tensors, 3x3 kernel, unit stride and dilation, C and K multiples of 8, y the size of x;
+ *    anything else returns UNSUPPORTED_DATATYPE / NOT_SUPPORTED.
+ *  - 32 * (K*C + tiles*C + tiles*K) bytes, tiles = N*ceil(H/2)*ceil(W/2), must fit AVOCADO_NO_ALLOC_SCRATCH_BYTES;
+ *    a larger problem returns AVOCADO_STATUS_BAD_PARAM and launches nothing.
+ *  - The first call on a device resolves the array's device address; make it before any stream capture.
+ *  - All calls on one device share the array: calls that overlap on the GPU race.  It keeps the last call's contents;
+ *    the only part that must start at zero, the kernel's 256-byte error word, is cleared by every call. */
+DLL_PUBLIC avStatus_t cudaConvolutionWinogradFusedForwardNoAlloc(avContextDescriptor_t context, const avConvolutionDescriptor_t config, const void *alpha1,
+		const avTensorDescriptor_t xDesc, const avMemoryDescriptor_t xMem, const avTensorDescriptor_t wDesc, const avMemoryDescriptor_t wMem,
+		const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem, const void *alpha2, const avTensorDescriptor_t zDesc,
+		const avMemoryDescriptor_t zMem, const void *beta, const avTensorDescriptor_t yDesc, avMemoryDescriptor_t yMem, avActivationType_t activation);
+
 #ifdef __cplusplus
 		} /* extern "C" */
 	} /* namespace backend */
