@@ -127,3 +127,36 @@ def test_golden_vectors():
         fresh = make_golden.compute(case)
         for key in fresh:
             assert np.array_equal(np.asarray(fresh[key]), data[key]), (case["name"], key)
+
+
+def test_oracle_matches_reference_kernel_outputs():
+    """tests/golden/reference_small.npz holds what the REFERENCE's own kernels (src/winograd_nonfused.cu compiled
+    unmodified into oracle/_ref, plus its cuBLAS GEMM wrapper) produced on a B200 for the seeded cases of
+    oracle/run_ref.py.  The oracle must reproduce every tensor of the forward and dW chains to the rounding of the
+    storage type; this is the pin of the oracle against the reference."""
+    from oracle import run_ref
+    data = np.load(os.path.join(GOLDEN, "reference_small.npz"))
+    rel = lambda a, b: np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+    for name in run_ref.SMALL:
+        dtype, ts, ks, n, h, w, c, k, _ = run_ref.CASES[name]
+        g = lambda key: data[name + "/" + key].astype(np.float64)
+        x_expected, w_expected, _, _ = run_ref.make_inputs(name)
+        assert np.array_equal(data[name + "/x"], x_expected) and np.array_equal(data[name + "/w"], w_expected)
+        pad = -(ks // 2)
+        eps = 2.0 ** -23 if dtype == "float32" else 2.0 ** -10
+        u = o.winograd_weight_transform(g("w"), ts)
+        v = o.winograd_input_transform(g("x"), ts, ks, padding=(pad, pad))
+        m = o.gemm_batched(v, u, trans_b=True)
+        assert rel(g("u"), u) <= 2 * eps, name
+        assert rel(g("v"), v) <= 2 * eps, name
+        assert rel(g("m"), m) <= 4 * eps, name
+        y = o.conv2d_forward(g("x"), g("w"), bias=g("bias"), padding=(pad, pad), activation="relu")
+        # the reference keeps fp16 matrices and fp16 arithmetic: F(4x4,3x3) in fp16 is only good to a few 1e-2
+        assert o.error_metrics(g("y"), y)["elem"] <= (1e-4 if dtype == "float32" else 6e-2), name
+        if dtype == "float32":
+            gr = o.winograd_gradient_transform(g("dy"), ts, ks)
+            mw = o.gemm_batched(gr, v, trans_a=True)
+            assert rel(g("g"), gr) <= 2 * eps, name
+            assert rel(g("mw"), mw) <= 8 * eps, name
+            dw = o.conv2d_backward_weights(g("x"), g("dy"), (ks, ks), (pad, pad))
+            assert o.error_metrics(g("dw"), dw)["elem"] <= 1e-4, name
