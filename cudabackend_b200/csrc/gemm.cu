@@ -24,6 +24,7 @@
 #include "device_utils.cuh"
 #include "umma.cuh"
 #include "winograd_internal.hpp"
+#include "gemm_internal.hpp"
 
 #include <cstdlib>
 #include <cstring>
@@ -160,14 +161,6 @@ namespace
 			}
 		}
 	}
-
-	struct GemmShape
-	{
-			int batch, M, N, Kc;
-			int lda, ldb, ldc;
-			long long strideA, strideB, strideC;
-			bool transA, transB;
-	};
 
 	template<typename T, typename AT, typename OT>
 	avStatus_t launch_simt(cudaStream_t stream, const GemmShape &s, const void *A, const void *B, void *C, AT alpha, AT beta)
@@ -584,7 +577,17 @@ namespace
 			{
 				if (abType != cType)
 					return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
-				return launch_simt<float, float, float>(stream, s, A, B, C, getAlphaValue<float>(alpha), getBetaValue<float>(beta));
+				const float a = getAlphaValue<float>(alpha);
+				const float b = getBetaValue<float>(beta);
+				if (forced_path() != 1)
+				{
+					const avStatus_t status = bk::launch_gemm_tf32(ctx, s, A, B, C, a, b);
+					if (status != AVOCADO_STATUS_NOT_SUPPORTED)
+						return status;
+				}
+				if (forced_path() == 2)
+					return AVOCADO_STATUS_NOT_SUPPORTED;
+				return launch_simt<float, float, float>(stream, s, A, B, C, a, b);
 			}
 			case AVOCADO_DTYPE_FLOAT64:
 			{

@@ -183,7 +183,7 @@ namespace umma
 	/* ---- descriptors ------------------------------------------------------------------------------------
 	 * Shared-memory matrix descriptor (64 bit): [13:0] start address >> 4, [29:16] leading byte offset >> 4,
 	 * [45:32] stride byte offset >> 4, [47:46] = 1 (Blackwell), [51:49] base offset, [63:61] swizzle mode. */
-	constexpr uint64_t kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6;
+	constexpr uint64_t kSwizzleNone = 0, kSwizzle128BBase32B = 1, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6;
 
 	__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smemAddr, uint32_t leadingBytes, uint32_t strideBytes, uint64_t swizzle)
 	{

@@ -108,3 +108,37 @@ def test_gemm_shape_mismatch(ctx):
     status = api.call_status("cudaGemmBatched", ctx.handle, api.GEMM_N, api.GEMM_T, None, A.desc.handle, A.mem.handle, B.desc.handle, B.mem.handle, None,
                              C.desc.handle, C.mem.handle)
     assert status == api.STATUS["BAD_PARAM"]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_gemm_batched_tensor_core_float32(ctx, shape, trans_b):
+    """float32 on the tensor cores: three TF32 passes over a hi/lo split must stay at float32-level accuracy"""
+    batch, m, n, k = shape
+    r = np.random.default_rng(16)
+    a = r.uniform(-1, 1, (batch, m, k))
+    b = r.normal(0, np.sqrt(2.0 / k), (batch, n, k) if trans_b else (batch, k, n))
+    c0 = np.full((batch, m, n), 7.0)
+    got, a64, b64, _ = run_gemm(ctx, "cudaGemmBatched", a, b, c0, "float32", False, trans_b, 1.25, None)
+    ref = o.gemm_batched(a64, b64, False, trans_b, alpha=1.25)
+    assert o.error_metrics(got, ref)["elem"] <= 2e-5
+
+
+# (batch, contraction length, rows of the result, columns of the result)
+TN_SHAPES = [(36, 392, 64, 64), (36, 6272, 64, 64), (4, 1000, 72, 200), (3, 77, 20, 36), (2, 33, 128, 64), (1, 4096, 256, 136)]
+
+
+@pytest.mark.parametrize("shape", TN_SHAPES)
+@pytest.mark.parametrize("beta", [None, 0.5])
+def test_gemm_batched_weight_gradient_contraction_float32(ctx, shape, beta):
+    """C = A^T * B with both operands stored contraction-index-outermost: the dW product of the Winograd backward pass"""
+    batch, kc, m, n = shape
+    r = np.random.default_rng(17)
+    a = r.uniform(-1, 1, (batch, kc, m))
+    b = r.uniform(-1, 1, (batch, kc, n))
+    c0 = r.uniform(-1, 1, (batch, m, n))
+    got, a64, b64, c64 = run_gemm(ctx, "cudaGemmBatched", a, b, c0, "float32", True, False, 0.75, beta)
+    ref = o.gemm_batched(a64, b64, True, False, alpha=0.75, beta=beta or 0.0, c=c64)
+    assert o.error_metrics(got, ref)["elem"] <= 2e-5
+    again, _, _, _ = run_gemm(ctx, "cudaGemmBatched", a, b, c0, "float32", True, False, 0.75, beta)
+    assert np.array_equal(got, again)  # fixed-order split reduction: bitwise reproducible
