@@ -39,6 +39,10 @@ CONFIGS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch (profiles/winograd_nonfused_f43_fp16_cfg2.txt)
+NCU_GEMM_TRAFFIC = {(2, "float16"): 58.123e6 + 9.621e6}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -61,7 +65,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -70,9 +74,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, window=None):
+        """Stops sampling; `window` = (t0, t1) in time.time() keeps only the samples taken inside the timed region."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -83,7 +88,9 @@ class ClockSampler:
             self.proc.kill()
         sm, sm_max, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for stamp, line in self.lines:
+            if window is not None and not (window[0] <= stamp <= window[1] + 0.05):
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -333,23 +340,25 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         else:
             full_step(i)
 
-    for i in range(args.warmup):
-        timed_step(i)
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        timed_step(i)
+    barrier()
     first = torch.cuda.Event(enable_timing=True)
     last = torch.cuda.Event(enable_timing=True)
     t_wall0 = time.perf_counter()
+    window0 = time.time()
     first.record(s0)
     for i in range(args.steps):
         timed_step(i)
     last.record(s0)
     sync_all()
+    window1 = time.time()
     elapsed_ms = first.elapsed_time(last)
     wall_ms = (time.perf_counter() - t_wall0) * 1e3
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop((window0, window1)) if rank == 0 else None
     if world > 1:
         t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -447,8 +456,12 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         sb = stage_bytes(cfg, matrices_dtype)
         gemm_s = stage_ms["gemm"] * 1e-3
         achieved = sb["gemm"] / gemm_s / 1e9
-        line["roofline"] = {"kernel": "kernel_gemm_nt_tc (transform-domain batched GEMM)", "bound": "hbm", "achieved": achieved,
-                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+        # DRAM bytes of one launch of this kernel from the committed ncu capture (cold caches); only known for the default workload
+        traffic = NCU_GEMM_TRAFFIC.get((args.config, matrices_dtype))
+        line["roofline"] = {"kernel": "kernel_gemm_nt_tc (transform-domain batched GEMM)" if matrices_dtype != "float32" else
+                            "kernel_gemm_nt_tf32x3 (transform-domain batched GEMM)", "bound": "hbm", "achieved": achieved,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
+                            "algorithmic_bytes": sb["gemm"],
                             "peak_source": peaks["source"], "tensor_tflops": sb["gemm_flops"] / gemm_s / 1e12,
                             "tensor_frac": sb["gemm_flops"] / gemm_s / 1e12 / peaks["bf16_tflops"]}
         line["stage_gbs"] = {name: sb[name] / (stage_ms[name] * 1e-3) / 1e9 for name in stage_names}
@@ -478,7 +491,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=2000)
+    parser.add_argument("--steps", type=int, default=10000)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
