@@ -15,6 +15,10 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <utility>
+#include <cuda_runtime.h>
 
 namespace bk
 {
@@ -100,6 +104,19 @@ namespace bk
 		return __float_as_int(v + 12582912.0f) - 0x4B400000;
 	}
 
+	/* Programmatic dependent launch: a kernel launched with launch_chained() may begin while the kernel before it on the
+	 * stream is still draining.  Everything it does before chain_wait() must touch only shared memory, TMEM and barriers;
+	 * chain_wait() returns once the previous kernel has completed and its writes are visible.  chain_release() lets the
+	 * next kernel on the stream start its own prologue.  Both are no-ops in a kernel launched the ordinary way. */
+	__device__ __forceinline__ void chain_wait()
+	{
+		asm volatile("griddepcontrol.wait;" ::: "memory");
+	}
+	__device__ __forceinline__ void chain_release()
+	{
+		asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+	}
+
 	template<typename CT>
 	__device__ __forceinline__ CT activation_forward(avocado::backend::avActivationType_t activation, CT x)
 	{
@@ -131,6 +148,37 @@ namespace bk
 	/* The same switch behind a call, for epilogues that are unrolled many times: inlining the transcendental cases into
 	 * every copy makes the loop body larger than the instruction cache even when only linear / relu ever run. */
 	__device__ __noinline__ float activation_forward_call(avocado::backend::avActivationType_t activation, float x);
+} /* namespace bk */
+
+namespace bk
+{
+	/* AVOCADO_B200_CHAIN=0 launches every kernel the ordinary way (for A/B timing) */
+	inline bool chained_launches_enabled()
+	{
+		static const bool enabled = []()
+		{
+			const char *env = std::getenv("AVOCADO_B200_CHAIN");
+			return not (env != nullptr and std::strcmp(env, "0") == 0);
+		}();
+		return enabled;
+	}
+	/* Launches a kernel that calls chain_wait() before its first global access, allowing it to overlap the tail of the
+	 * previous kernel on the stream. */
+	template<typename ... KernelArgs, typename ... Args>
+	cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t sharedBytes, cudaStream_t stream, Args &&... args)
+	{
+		cudaLaunchConfig_t config = { };
+		config.gridDim = grid;
+		config.blockDim = block;
+		config.dynamicSmemBytes = sharedBytes;
+		config.stream = stream;
+		cudaLaunchAttribute attribute[1];
+		attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attribute[0].val.programmaticStreamSerializationAllowed = chained_launches_enabled() ? 1 : 0;
+		config.attrs = attribute;
+		config.numAttrs = 1;
+		return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+	}
 } /* namespace bk */
 
 #endif /* B200_DEVICE_UTILS_CUH_ */

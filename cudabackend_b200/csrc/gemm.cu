@@ -251,6 +251,9 @@ namespace
 		umma::tcgen05_fence_after();
 		const uint32_t tmem_base = tmem_base_slot;
 		volatile int *abort_ptr = &abort_flag;
+		/* barriers, TMEM and descriptors are ready: only now wait for the kernel that produces A (and may still read C) */
+		chain_wait();
+		chain_release();
 
 		if (warp == 0)
 		{
@@ -455,8 +458,10 @@ namespace
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
 		const int ctasPerSm = (Cfg::kSmemBytes <= 110 * 1024 and Cfg::kTmemColumns <= 256) ? 2 : 1;
 		const int grid = static_cast<int>(std::min<long long>(tiles, static_cast<long long>(sms) * ctasPerSm));
-		kernel<<<grid, kTcThreads, Cfg::kSmemBytes, ctx.getStream()>>>(mapA, mapB, mapC, mBlocks, nBlocks, kBlocks, static_cast<int>(tiles), s.N, alpha,
-				deviceStatus);
+		const cudaError_t launched = launch_chained(kernel, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, ctx.getStream(), mapA, mapB, mapC, mBlocks,
+				nBlocks, kBlocks, static_cast<int>(tiles), s.N, alpha, deviceStatus);
+		if (launched != cudaSuccess)
+			return convertStatus(launched);
 		return checkForErrors();
 	}
 

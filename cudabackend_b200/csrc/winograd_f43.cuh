@@ -107,6 +107,9 @@ namespace f43
 	constexpr int kChannelBlock = 64; /* channels per strip: one warp, two channels per lane */
 	constexpr int kThreads = 256;
 	constexpr int kMaxStages = 4;
+#ifndef F43_OUT_BLOCKS
+#define F43_OUT_BLOCKS 3
+#endif
 
 	struct InputGeometry
 	{
@@ -146,6 +149,8 @@ namespace f43
 			umma::prefetch_tensormap(&mapX);
 		}
 		__syncthreads();
+		chain_wait(); /* x and the transform-domain tensor may still be in use by the previous kernel */
+		chain_release();
 
 		auto issue = [&](int item, int stage)
 		{
@@ -267,11 +272,13 @@ namespace f43
 
 	/* ACT: 0 linear, 1 relu, 2 any (run-time switch) */
 	template<typename T, typename MT, int ACT>
-	__global__ void __launch_bounds__(kThreads, 2) kernel_output(const MT *__restrict__ matrices, T *output, PlaneGeometry g, const float *__restrict__ bias,
+	__global__ void __launch_bounds__(kThreads, F43_OUT_BLOCKS) kernel_output(const MT *__restrict__ matrices, T *output, PlaneGeometry g, const float *__restrict__ bias,
 			const T *__restrict__ ext, float alpha1, float alpha2, float beta, avocado::backend::avActivationType_t activation)
 	{
 		using PT = typename Pair<T>::type;
 		using PM = typename Pair<MT>::type;
+		chain_wait();
+		chain_release();
 		/* one warp per tile and block of 64 channels: blockIdx.x counts groups of 8 tiles, blockIdx.y channel blocks */
 		const unsigned int tile = blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
 		const int c0 = blockIdx.y * kChannelBlock + 2 * (threadIdx.x % 32);
@@ -375,6 +382,8 @@ namespace f43
 	{
 		using PT = typename Pair<T>::type;
 		using PM = typename Pair<MT>::type;
+		chain_wait();
+		chain_release();
 		/* one warp per tile and block of 64 channels: blockIdx.x counts groups of 8 tiles, blockIdx.y channel blocks */
 		const unsigned int tile = blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
 		const int c0 = blockIdx.y * kChannelBlock + 2 * (threadIdx.x % 32);

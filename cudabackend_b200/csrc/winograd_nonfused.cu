@@ -55,6 +55,8 @@ namespace
 	{
 		using CT = typename ComputeType<T>::type;
 		using M = Matrix<Transform::Weight, TS, KS>;
+		chain_wait();
+		chain_release();
 		const int cvecs = filtersIn / VEC;
 		const long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
 		if (g >= static_cast<long long>(filtersOut) * cvecs)
@@ -393,7 +395,7 @@ namespace
 		const int vec = pick_vec<T, MT>(C, sizeof(T) == 8 ? 1 : 2, { wPtr }, { matricesPtr });
 		const unsigned int grid = blocks_for(static_cast<long long>(K) * (C / vec));
 		DISPATCH_TILE(ks, transformSize,
-				DISPATCH_VEC2(vec, kernel_weight_transform<TS, KS, T, MT, VEC> <<<grid, kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(wPtr), K, C, invert);))
+				DISPATCH_VEC2(vec, launch_chained(kernel_weight_transform<TS, KS, T, MT, VEC>, dim3(grid), dim3(kThreads), 0, ctx.getStream(), reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(wPtr), K, C, invert);))
 		return checkForErrors();
 	}
 
@@ -479,22 +481,25 @@ namespace
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 
 		auto kernel = f43::kernel_input_tma<T, MT>;
-		constexpr int ring_budget = 96 * 1024;
+		static const int ring_budget = std::getenv("F43_RING") ? std::atoi(std::getenv("F43_RING")) * 1024 : 96 * 1024;
 		g.stages = std::max(2, std::min(f43::kMaxStages, ring_budget / g.stage_bytes));
 		const int smem_bytes = g.stages * g.stage_bytes + 128;
 		static bool configured[kMaxDevices] = { };
 		if (not configured[ctx.device])
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + 128) != cudaSuccess)
+			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024 + 128) != cudaSuccess)
 				return checkForErrors();
 			configured[ctx.device] = true;
 		}
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
 		const int threads = 32 * std::min(8, g.strip_tiles_h * g.strip_tiles_w);
-		const int ctas_per_sm = std::max(1, std::min(3, (220 * 1024) / (smem_bytes + 1024)));
+		const int ctas_per_sm = std::max(1, std::min(4, (220 * 1024) / (smem_bytes + 1024)));
 		const int grid = std::min(g.num_items, ctas_per_sm * sms);
-		kernel<<<grid, threads, smem_bytes, ctx.getStream()>>>(map, reinterpret_cast<MT*>(matricesPtr), g, ctx.getDeviceStatus());
+		const cudaError_t launched = launch_chained(kernel, dim3(grid), dim3(threads), smem_bytes, ctx.getStream(), map, reinterpret_cast<MT*>(matricesPtr), g,
+				ctx.getDeviceStatus());
+		if (launched != cudaSuccess)
+			return convertStatus(launched);
 		return checkForErrors();
 	}
 
@@ -530,11 +535,11 @@ namespace
 		const T *z = reinterpret_cast<const T*>(zPtr);
 		cudaStream_t stream = ctx.getStream();
 		if (activation == AVOCADO_ACTIVATION_LINEAR)
-			f43::kernel_output<T, MT, 0> <<<grid, f43::kThreads, 0, stream>>>(m, y, g, b, z, alpha1, alpha2, beta, activation);
+			launch_chained(f43::kernel_output<T, MT, 0>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
 		else if (activation == AVOCADO_ACTIVATION_RELU)
-			f43::kernel_output<T, MT, 1> <<<grid, f43::kThreads, 0, stream>>>(m, y, g, b, z, alpha1, alpha2, beta, activation);
+			launch_chained(f43::kernel_output<T, MT, 1>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
 		else
-			f43::kernel_output<T, MT, 2> <<<grid, f43::kThreads, 0, stream>>>(m, y, g, b, z, alpha1, alpha2, beta, activation);
+			launch_chained(f43::kernel_output<T, MT, 2>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
 		return checkForErrors();
 	}
 
