@@ -1,6 +1,6 @@
 /*
- * winograd_f43.cuh -- fast kernels for the F(4x4,3x3) transforms on 16-bit and float32 tensors, the case the
- * ResNet-style layers use.  Same arithmetic as the generic kernels of winograd_nonfused.cu (reference
+ * winograd_f43.cuh -- fast kernels for the 3x3 transforms, F(4x4,3x3) and F(2x2,3x3), on 16-bit and float32 tensors,
+ * the case the ResNet-style layers use.  Same arithmetic as the generic kernels of winograd_nonfused.cu (reference
  * src/winograd_nonfused.cu:302-423, tables :549-557) with the 6-point transforms factored by hand:
  *
  *   B^T d :  c = d4-d2, e = d3-d1, a = d2-d4/4, b = d1-d3/4
@@ -65,6 +65,27 @@ namespace f43
 		o[5] = 2.0f * g[3];
 	}
 
+	/* F(2x2,3x3) one-dimensional transforms (reference tables src/winograd_nonfused.cu:534-539) */
+	__device__ __forceinline__ void input_1d(const float (&d)[4], float (&o)[4])
+	{
+		o[0] = d[0] - d[2];
+		o[1] = d[1] + d[2];
+		o[2] = d[2] - d[1];
+		o[3] = d[3] - d[1];
+	}
+	__device__ __forceinline__ void output_1d(const float (&m)[4], float (&o)[2])
+	{
+		o[0] = fmaf(0.5f, m[1] + m[2], m[0]);
+		o[1] = fmaf(0.5f, m[1] - m[2], m[3]);
+	}
+	__device__ __forceinline__ void gradient_1d(const float (&g)[2], float (&o)[4])
+	{
+		o[0] = g[0];
+		o[1] = g[0] + g[1];
+		o[2] = g[0] - g[1];
+		o[3] = g[1];
+	}
+
 	/* two adjacent channels in storage form */
 	template<typename T> struct Pair;
 	template<> struct Pair<half>
@@ -117,14 +138,14 @@ namespace f43
 			int pad_h, pad_w;
 			int strip_tiles_h, strip_tiles_w; /* tiles per strip */
 			int row_groups, w_segments, c_blocks;
-			int box_w; /* pixels per box row = 4 * strip_tiles_w + 2 */
+			int box_w; /* pixels per box row = transformSize * strip_tiles_w + 2 */
 			int stage_bytes;
 			int stages; /* depth of the shared-memory ring, 2..kMaxStages */
 			int num_items;
 			long long nb_tiles;
 	};
 
-	template<typename T, typename MT>
+	template<int TS, typename T, typename MT>
 	__global__ void __launch_bounds__(kThreads, 3) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
 			int *deviceStatus)
 	{
@@ -159,8 +180,8 @@ namespace f43
 			const int rg = (item / (g.c_blocks * g.w_segments)) % g.row_groups;
 			const int n = item / (g.c_blocks * g.w_segments * g.row_groups);
 			umma::mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>(g.stage_bytes));
-			umma::tma_load_4d(smem + stage * g.stage_bytes, &mapX, &full_bar[stage], cb * kChannelBlock, g.pad_w + ws * g.strip_tiles_w * 4,
-					g.pad_h + rg * g.strip_tiles_h * 4, n);
+			umma::tma_load_4d(smem + stage * g.stage_bytes, &mapX, &full_bar[stage], cb * kChannelBlock, g.pad_w + ws * g.strip_tiles_w * TS,
+					g.pad_h + rg * g.strip_tiles_h * TS, n);
 		};
 
 		/* fill the ring: strips 0 .. stages-2 of this CTA are requested before the first one is consumed */
@@ -211,46 +232,47 @@ namespace f43
 				const int tw = ws * g.strip_tiles_w + tc;
 				if (th >= g.tiles_h or tw >= g.tiles_w or c0 >= g.channels)
 					continue;
-				const T *src = box + (tr * 4) * row_pitch + (tc * 4) * kChannelBlock + 2 * lane;
+				constexpr int TL = TS + 2;
+				const T *src = box + (tr * TS) * row_pitch + (tc * TS) * kChannelBlock + 2 * lane;
 
-				float tmp[2][36]; /* B^T d, per channel */
+				float tmp[2][TL * TL]; /* B^T d, per channel */
 #pragma unroll
-				for (int c = 0; c < 6; c++)
+				for (int c = 0; c < TL; c++)
 				{
-					float col0[6], col1[6];
+					float col0[TL], col1[TL];
 #pragma unroll
-					for (int r = 0; r < 6; r++)
+					for (int r = 0; r < TL; r++)
 					{
 						const float2 v = Pair<T>::unpack(*reinterpret_cast<const PT*>(src + r * row_pitch + c * kChannelBlock));
 						col0[r] = v.x;
 						col1[r] = v.y;
 					}
-					float o0[6], o1[6];
+					float o0[TL], o1[TL];
 					input_1d(col0, o0);
 					input_1d(col1, o1);
 #pragma unroll
-					for (int i = 0; i < 6; i++)
+					for (int i = 0; i < TL; i++)
 					{
-						tmp[0][i * 6 + c] = o0[i];
-						tmp[1][i * 6 + c] = o1[i];
+						tmp[0][i * TL + c] = o0[i];
+						tmp[1][i * TL + c] = o1[i];
 					}
 				}
 				const long long tile = (static_cast<long long>(n) * g.tiles_h + th) * g.tiles_w + tw;
 				MT *dst = matrices + static_cast<size_t>(tile) * g.channels + c0;
 #pragma unroll
-				for (int i = 0; i < 6; i++)
+				for (int i = 0; i < TL; i++)
 				{
-					float row0[6], row1[6], o0[6], o1[6];
+					float row0[TL], row1[TL], o0[TL], o1[TL];
 #pragma unroll
-					for (int c = 0; c < 6; c++)
+					for (int c = 0; c < TL; c++)
 					{
-						row0[c] = tmp[0][i * 6 + c];
-						row1[c] = tmp[1][i * 6 + c];
+						row0[c] = tmp[0][i * TL + c];
+						row1[c] = tmp[1][i * TL + c];
 					}
 					input_1d(row0, o0);
 					input_1d(row1, o1);
 #pragma unroll
-					for (int j = 0; j < 6; j++)
+					for (int j = 0; j < TL; j++)
 					{
 						*reinterpret_cast<PM*>(dst) = Pair<MT>::pack(o0[j], o1[j]);
 						dst += plane_stride;
@@ -271,7 +293,7 @@ namespace f43
 	};
 
 	/* ACT: 0 linear, 1 relu, 2 any (run-time switch) */
-	template<typename T, typename MT, int ACT>
+	template<int TS, typename T, typename MT, int ACT>
 	__global__ void __launch_bounds__(kThreads, F43_OUT_BLOCKS) kernel_output(const MT *__restrict__ matrices, T *output, PlaneGeometry g, const float *__restrict__ bias,
 			const T *__restrict__ ext, float alpha1, float alpha2, float beta, avocado::backend::avActivationType_t activation)
 	{
@@ -289,59 +311,60 @@ namespace f43
 		const int n = static_cast<int>(tile_row / static_cast<unsigned int>(g.tiles_h));
 		const int th = static_cast<int>(tile_row - n * g.tiles_h);
 
+		constexpr int TL = TS + 2;
 		const size_t plane_stride = static_cast<size_t>(g.nb_tiles) * g.channels;
 		const MT *src = matrices + static_cast<size_t>(tile) * g.channels + c0;
-		PM raw[36];
+		PM raw[TL * TL];
 #pragma unroll
-		for (int p = 0; p < 36; p++)
+		for (int p = 0; p < TL * TL; p++)
 		{
 			raw[p] = *reinterpret_cast<const PM*>(src);
 			src += plane_stride;
 		}
-		float tmp[2][24]; /* A^T M: 4 x 6 per channel */
+		float tmp[2][TS * TL]; /* A^T M: TS x TL per channel */
 #pragma unroll
-		for (int c = 0; c < 6; c++)
+		for (int c = 0; c < TL; c++)
 		{
-			float col0[6], col1[6], o0[4], o1[4];
+			float col0[TL], col1[TL], o0[TS], o1[TS];
 #pragma unroll
-			for (int r = 0; r < 6; r++)
+			for (int r = 0; r < TL; r++)
 			{
-				const float2 v = Pair<MT>::unpack(raw[r * 6 + c]);
+				const float2 v = Pair<MT>::unpack(raw[r * TL + c]);
 				col0[r] = v.x;
 				col1[r] = v.y;
 			}
 			output_1d(col0, o0);
 			output_1d(col1, o1);
 #pragma unroll
-			for (int i = 0; i < 4; i++)
+			for (int i = 0; i < TS; i++)
 			{
-				tmp[0][i * 6 + c] = o0[i];
-				tmp[1][i * 6 + c] = o1[i];
+				tmp[0][i * TL + c] = o0[i];
+				tmp[1][i * TL + c] = o1[i];
 			}
 		}
 		float2 b = make_float2(0.0f, 0.0f);
 		if (bias != nullptr)
 			b = *reinterpret_cast<const float2*>(bias + c0);
 
-		const int h0 = th * 4, w0 = tw * 4;
+		const int h0 = th * TS, w0 = tw * TS;
 		T *tile_ptr = output + ((static_cast<size_t>(n) * g.height + h0) * g.width + w0) * g.channels + c0;
 		const T *ext_ptr = (ext == nullptr) ? nullptr : ext + ((static_cast<size_t>(n) * g.height + h0) * g.width + w0) * g.channels + c0;
 		const int row_stride = g.width * g.channels;
-		const bool interior = (h0 + 4 <= g.height) and (w0 + 4 <= g.width);
+		const bool interior = (h0 + TS <= g.height) and (w0 + TS <= g.width);
 #pragma unroll
-		for (int i = 0; i < 4; i++)
+		for (int i = 0; i < TS; i++)
 		{
-			float row0[6], row1[6], o0[4], o1[4];
+			float row0[TL], row1[TL], o0[TS], o1[TS];
 #pragma unroll
-			for (int c = 0; c < 6; c++)
+			for (int c = 0; c < TL; c++)
 			{
-				row0[c] = tmp[0][i * 6 + c];
-				row1[c] = tmp[1][i * 6 + c];
+				row0[c] = tmp[0][i * TL + c];
+				row1[c] = tmp[1][i * TL + c];
 			}
 			output_1d(row0, o0);
 			output_1d(row1, o1);
 #pragma unroll
-			for (int j = 0; j < 4; j++)
+			for (int j = 0; j < TS; j++)
 			{
 				if (interior or (h0 + i < g.height and w0 + j < g.width))
 				{
@@ -376,8 +399,8 @@ namespace f43
 		}
 	}
 
-	/* dy[N,H,W,K] -> [36, tiles, K]: 4x4 tile, zero past the image edge (reference src/winograd_nonfused.cu:424-475) */
-	template<typename T, typename MT>
+	/* dy[N,H,W,K] -> [tile*tile, tiles, K]: TS x TS tile, zero past the image edge (reference src/winograd_nonfused.cu:424-475) */
+	template<int TS, typename T, typename MT>
 	__global__ void __launch_bounds__(kThreads, 2) kernel_gradient(MT *__restrict__ matrices, const T *__restrict__ gradient, PlaneGeometry g)
 	{
 		using PT = typename Pair<T>::type;
@@ -393,59 +416,60 @@ namespace f43
 		const int tw = static_cast<int>(tile - tile_row * g.tiles_w);
 		const int n = static_cast<int>(tile_row / static_cast<unsigned int>(g.tiles_h));
 		const int th = static_cast<int>(tile_row - n * g.tiles_h);
-		const int h0 = th * 4, w0 = tw * 4;
+		constexpr int TL = TS + 2;
+		const int h0 = th * TS, w0 = tw * TS;
 		const T *tile_ptr = gradient + ((static_cast<size_t>(n) * g.height + h0) * g.width + w0) * g.channels + c0;
 		const int row_stride = g.width * g.channels;
-		const bool interior = (h0 + 4 <= g.height) and (w0 + 4 <= g.width);
+		const bool interior = (h0 + TS <= g.height) and (w0 + TS <= g.width);
 
-		PT raw[16];
+		PT raw[TS * TS];
 #pragma unroll
-		for (int r = 0; r < 4; r++)
+		for (int r = 0; r < TS; r++)
 #pragma unroll
-			for (int c = 0; c < 4; c++)
+			for (int c = 0; c < TS; c++)
 			{
 				if (interior or (h0 + r < g.height and w0 + c < g.width))
-					raw[r * 4 + c] = *reinterpret_cast<const PT*>(tile_ptr + r * row_stride + c * g.channels);
+					raw[r * TS + c] = *reinterpret_cast<const PT*>(tile_ptr + r * row_stride + c * g.channels);
 				else
-					raw[r * 4 + c] = Pair<T>::pack(0.0f, 0.0f);
+					raw[r * TS + c] = Pair<T>::pack(0.0f, 0.0f);
 			}
-		float tmp[2][24]; /* G' g: 6 x 4 per channel */
+		float tmp[2][TL * TS]; /* G' g: TL x TS per channel */
 #pragma unroll
-		for (int c = 0; c < 4; c++)
+		for (int c = 0; c < TS; c++)
 		{
-			float col0[4], col1[4], o0[6], o1[6];
+			float col0[TS], col1[TS], o0[TL], o1[TL];
 #pragma unroll
-			for (int r = 0; r < 4; r++)
+			for (int r = 0; r < TS; r++)
 			{
-				const float2 v = Pair<T>::unpack(raw[r * 4 + c]);
+				const float2 v = Pair<T>::unpack(raw[r * TS + c]);
 				col0[r] = v.x;
 				col1[r] = v.y;
 			}
 			gradient_1d(col0, o0);
 			gradient_1d(col1, o1);
 #pragma unroll
-			for (int i = 0; i < 6; i++)
+			for (int i = 0; i < TL; i++)
 			{
-				tmp[0][i * 4 + c] = o0[i];
-				tmp[1][i * 4 + c] = o1[i];
+				tmp[0][i * TS + c] = o0[i];
+				tmp[1][i * TS + c] = o1[i];
 			}
 		}
 		const size_t plane_stride = static_cast<size_t>(g.nb_tiles) * g.channels;
 		MT *dst = matrices + static_cast<size_t>(tile) * g.channels + c0;
 #pragma unroll
-		for (int i = 0; i < 6; i++)
+		for (int i = 0; i < TL; i++)
 		{
-			float row0[4], row1[4], o0[6], o1[6];
+			float row0[TS], row1[TS], o0[TL], o1[TL];
 #pragma unroll
-			for (int c = 0; c < 4; c++)
+			for (int c = 0; c < TS; c++)
 			{
-				row0[c] = tmp[0][i * 4 + c];
-				row1[c] = tmp[1][i * 4 + c];
+				row0[c] = tmp[0][i * TS + c];
+				row1[c] = tmp[1][i * TS + c];
 			}
 			gradient_1d(row0, o0);
 			gradient_1d(row1, o1);
 #pragma unroll
-			for (int j = 0; j < 6; j++)
+			for (int j = 0; j < TL; j++)
 			{
 				*reinterpret_cast<PM*>(dst) = Pair<MT>::pack(o0[j], o1[j]);
 				dst += plane_stride;

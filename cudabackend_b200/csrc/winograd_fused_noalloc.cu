@@ -150,7 +150,7 @@ namespace avocado
 				avStatus_t status = bk::winograd_weight_transform(ctx, conv, 2, w, wPtr, u, u_ptr);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;
-				status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr);
+				status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr, status_word);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;
 				status = bk::gemm_batched_nt_tensor_core(ctx, v, v_ptr, u, u_ptr, m, m_ptr, status_word);

@@ -13,9 +13,10 @@ namespace bk
 	avocado::backend::avStatus_t winograd_weight_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
 			int transformSize, const avocado::backend::b200::TensorObject &w, const void *wPtr, const avocado::backend::b200::TensorObject &m, void *mPtr);
 
+	/* deviceStatus: where the TMA-staged kernel reports a wait that ran out; null = the context's own status word */
 	avocado::backend::avStatus_t winograd_input_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
 			int transformSize, const avocado::backend::b200::TensorObject &w, const avocado::backend::b200::TensorObject &x, const void *xPtr,
-			const avocado::backend::b200::TensorObject &m, void *mPtr);
+			const avocado::backend::b200::TensorObject &m, void *mPtr, int *deviceStatus = nullptr);
 
 	avocado::backend::avStatus_t winograd_output_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
 			int transformSize, const avocado::backend::b200::TensorObject &w, const void *alpha1, const avocado::backend::b200::TensorObject &m,

@@ -437,22 +437,24 @@ namespace
 			static constexpr CUtensorMapDataType value = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
 	};
 
-	template<typename T, typename MT>
-	avStatus_t launch_f43_input(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr)
+	template<int TS, typename T, typename MT>
+	avStatus_t launch_f43_input(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
+			int *deviceStatus)
 	{
 		if (cuda_sm_version(ctx.device) != 100 or not config.paddingValueIsZero())
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		if ((geo.channels * sizeof(T)) % 16 != 0 or not aligned_to(xPtr, 16) or not aligned_to(matricesPtr, 2 * sizeof(MT)))
 			return AVOCADO_STATUS_NOT_SUPPORTED;
-		/* a strip is at most 8 tiles (one per warp) and its halo box at most 48 KB */
+		/* a strip's halo box is at most 48 KB; F(4x4) strips hold at most 8 tiles (one per warp), F(2x2) strips up to 32 */
 		const int max_pixels = 48 * 1024 / (f43::kChannelBlock * static_cast<int>(sizeof(T)));
-		const int max_tw = std::min(8, (max_pixels / 6 - 2) / 4);
+		const int max_tiles = (TS == 4) ? 8 : 32;
+		const int max_tw = std::min((TS == 4) ? 8 : 16, (max_pixels / (TS + 2) - 2) / TS);
 		const int segments = (geo.tiles_w + max_tw - 1) / max_tw;
 		f43::InputGeometry g;
 		g.strip_tiles_w = (geo.tiles_w + segments - 1) / segments;
-		g.box_w = 4 * g.strip_tiles_w + 2;
-		g.strip_tiles_h = std::max(1, std::min(std::min(geo.tiles_h, 8 / g.strip_tiles_w), (max_pixels / g.box_w - 2) / 4));
-		const int box_h = 4 * g.strip_tiles_h + 2;
+		g.box_w = TS * g.strip_tiles_w + 2;
+		g.strip_tiles_h = std::max(1, std::min(std::min(geo.tiles_h, max_tiles / g.strip_tiles_w), (max_pixels / g.box_w - 2) / TS));
+		const int box_h = TS * g.strip_tiles_h + 2;
 		if (g.box_w > 256 or box_h > 256)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		g.batch = geo.batch;
@@ -480,7 +482,7 @@ namespace
 		if (not umma::make_tensor_map(&map, TmaType<T>::value, 4, const_cast<void*>(xPtr), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 
-		auto kernel = f43::kernel_input_tma<T, MT>;
+		auto kernel = f43::kernel_input_tma<TS, T, MT>;
 		static const int ring_budget = std::getenv("F43_RING") ? std::atoi(std::getenv("F43_RING")) * 1024 : 96 * 1024;
 		g.stages = std::max(2, std::min(f43::kMaxStages, ring_budget / g.stage_bytes));
 		const int smem_bytes = g.stages * g.stage_bytes + 128;
@@ -497,7 +499,7 @@ namespace
 		const int ctas_per_sm = std::max(1, std::min(4, (220 * 1024) / (smem_bytes + 1024)));
 		const int grid = std::min(g.num_items, ctas_per_sm * sms);
 		const cudaError_t launched = launch_chained(kernel, dim3(grid), dim3(threads), smem_bytes, ctx.getStream(), map, reinterpret_cast<MT*>(matricesPtr), g,
-				ctx.getDeviceStatus());
+				deviceStatus != nullptr ? deviceStatus : ctx.getDeviceStatus());
 		if (launched != cudaSuccess)
 			return convertStatus(launched);
 		return checkForErrors();
@@ -516,7 +518,7 @@ namespace
 		return g;
 	}
 
-	template<typename T, typename MT>
+	template<int TS, typename T, typename MT>
 	avStatus_t launch_f43_output(ContextObject &ctx, const ConvGeometry &geo, const void *matricesPtr, void *yPtr, const void *bPtr, const void *zPtr,
 			float alpha1, float alpha2, float beta, avActivationType_t activation)
 	{
@@ -535,15 +537,15 @@ namespace
 		const T *z = reinterpret_cast<const T*>(zPtr);
 		cudaStream_t stream = ctx.getStream();
 		if (activation == AVOCADO_ACTIVATION_LINEAR)
-			launch_chained(f43::kernel_output<T, MT, 0>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
+			launch_chained(f43::kernel_output<TS, T, MT, 0>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
 		else if (activation == AVOCADO_ACTIVATION_RELU)
-			launch_chained(f43::kernel_output<T, MT, 1>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
+			launch_chained(f43::kernel_output<TS, T, MT, 1>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
 		else
-			launch_chained(f43::kernel_output<T, MT, 2>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
+			launch_chained(f43::kernel_output<TS, T, MT, 2>, grid, dim3(f43::kThreads), 0, stream, m, y, g, b, z, alpha1, alpha2, beta, activation);
 		return checkForErrors();
 	}
 
-	template<typename T, typename MT>
+	template<int TS, typename T, typename MT>
 	avStatus_t launch_f43_gradient(ContextObject &ctx, const ConvGeometry &geo, const void *dyPtr, void *matricesPtr)
 	{
 		if (geo.channels % 2 != 0 or not aligned_to(matricesPtr, 2 * sizeof(MT)) or not aligned_to(dyPtr, 2 * sizeof(T)))
@@ -554,7 +556,7 @@ namespace
 		if (g.nb_tiles > 0x7FFFFFFFll or geo.channels > 65535 * f43::kChannelBlock)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		const dim3 grid(static_cast<unsigned int>((g.nb_tiles + 7) / 8), (geo.channels + f43::kChannelBlock - 1) / f43::kChannelBlock);
-		f43::kernel_gradient<T, MT> <<<grid, f43::kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(dyPtr), g);
+		f43::kernel_gradient<TS, T, MT> <<<grid, f43::kThreads, 0, ctx.getStream()>>>(reinterpret_cast<MT*>(matricesPtr), reinterpret_cast<const T*>(dyPtr), g);
 		return checkForErrors();
 	}
 
@@ -571,36 +573,37 @@ namespace
 
 
 	/* float64 has no fast kernel: these wrappers keep the double instantiations out of the fast templates */
-	template<typename T, typename MT>
-	avStatus_t launch_f43_input_if(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr)
+	template<int TS, typename T, typename MT>
+	avStatus_t launch_f43_input_if(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
+			int *deviceStatus)
 	{
 		if constexpr (sizeof(T) <= 4)
-			return launch_f43_input<T, MT>(ctx, config, geo, xPtr, matricesPtr);
+			return launch_f43_input<TS, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus);
 		else
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 	}
-	template<typename T, typename MT>
+	template<int TS, typename T, typename MT>
 	avStatus_t launch_f43_output_if(ContextObject &ctx, const ConvGeometry &geo, const void *matricesPtr, void *yPtr, const void *bPtr, const void *zPtr,
 			double alpha1, double alpha2, double beta, avActivationType_t activation)
 	{
 		if constexpr (sizeof(T) <= 4)
-			return launch_f43_output<T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, static_cast<float>(alpha1), static_cast<float>(alpha2),
+			return launch_f43_output<TS, T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, static_cast<float>(alpha1), static_cast<float>(alpha2),
 					static_cast<float>(beta), activation);
 		else
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 	}
-	template<typename T, typename MT>
+	template<int TS, typename T, typename MT>
 	avStatus_t launch_f43_gradient_if(ContextObject &ctx, const ConvGeometry &geo, const void *dyPtr, void *matricesPtr)
 	{
 		if constexpr (sizeof(T) <= 4)
-			return launch_f43_gradient<T, MT>(ctx, geo, dyPtr, matricesPtr);
+			return launch_f43_gradient<TS, T, MT>(ctx, geo, dyPtr, matricesPtr);
 		else
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 	}
 
 	template<typename T, typename MT>
 	avStatus_t launch_input_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const TensorObject &xDesc,
-			const void *xPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize)
+			const void *xPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize, int *deviceStatus)
 	{
 		using CT = typename ComputeType<T>::type;
 		if (xDesc.nb_dims != 4)
@@ -611,9 +614,10 @@ namespace
 			return AVOCADO_STATUS_BAD_PARAM;
 		if (geo.nb_tiles() == 0 or geo.channels == 0)
 			return AVOCADO_STATUS_SUCCESS;
-		if (transformSize == 4 and ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
+		if (ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
 		{
-			const avStatus_t fast = launch_f43_input_if<T, MT>(ctx, config, geo, xPtr, matricesPtr);
+			const avStatus_t fast = (transformSize == 4) ? launch_f43_input_if<4, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus) :
+					launch_f43_input_if<2, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus);
 			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
 				return fast;
 		}
@@ -637,9 +641,10 @@ namespace
 			return AVOCADO_STATUS_BAD_PARAM;
 		if (geo.nb_tiles() == 0 or geo.channels == 0)
 			return AVOCADO_STATUS_SUCCESS;
-		if (transformSize == 4 and ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
+		if (ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
 		{
-			const avStatus_t fast = launch_f43_gradient_if<T, MT>(ctx, geo, dyPtr, matricesPtr);
+			const avStatus_t fast = (transformSize == 4) ? launch_f43_gradient_if<4, T, MT>(ctx, geo, dyPtr, matricesPtr) :
+					launch_f43_gradient_if<2, T, MT>(ctx, geo, dyPtr, matricesPtr);
 			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
 				return fast;
 		}
@@ -667,9 +672,10 @@ namespace
 		const CT a1 = getAlphaValue<CT>(alpha1);
 		const CT a2 = getAlphaValue<CT>(alpha2);
 		const CT b = getBetaValue<CT>(beta);
-		if (transformSize == 4 and ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
+		if (ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
 		{
-			const avStatus_t fast = launch_f43_output_if<T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, a1, a2, b, activation);
+			const avStatus_t fast = (transformSize == 4) ? launch_f43_output_if<4, T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, a1, a2, b, activation) :
+					launch_f43_output_if<2, T, MT>(ctx, geo, matricesPtr, yPtr, bPtr, zPtr, a1, a2, b, activation);
 			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
 				return fast;
 		}
@@ -759,7 +765,7 @@ namespace bk
 	}
 
 	avStatus_t winograd_input_transform(ContextObject &ctx, const ConvolutionObject &conv, int transformSize, const TensorObject &w, const TensorObject &x, const void *xPtr,
-			const TensorObject &m, void *mPtr)
+			const TensorObject &m, void *mPtr, int *deviceStatus)
 	{
 		if (not tile_config_supported(w, transformSize))
 			return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
@@ -772,19 +778,19 @@ namespace bk
 		switch (classify(w.dtype, m.dtype))
 		{
 			case Pairing::F16_F16:
-				return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			case Pairing::F16_F32:
-				return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			case Pairing::BF16_BF16:
-				return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			case Pairing::BF16_F16:
-				return launch_input_transform<__nv_bfloat16, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<__nv_bfloat16, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			case Pairing::BF16_F32:
-				return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			case Pairing::F32_F32:
-				return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			case Pairing::F64_F64:
-				return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize);
+				return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
 			default:
 				return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
 		}
