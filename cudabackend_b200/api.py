@@ -81,6 +81,7 @@ SIGNATURES = {
     "cudaContextLaunchGraph": (_INT, [_H, _I64]),
     "cudaDestroyCapturedGraph": (_INT, [_I64]),
     "cudaConvolutionWinogradFusedForwardNoAlloc": (_INT, _conv_args),
+    "cudaRunBoundedWaitSelfTest": (_INT, [_H, _INT]),
 }
 
 # exported for link compatibility, return NOT_SUPPORTED

@@ -26,6 +26,9 @@
 #include "winograd_internal.hpp"
 #include "gemm_internal.hpp"
 
+#include <Avocado/cuda_backend_ext.h>
+
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
@@ -602,6 +605,50 @@ namespace
 			}
 			default:
 				return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
+		}
+	}
+}
+
+namespace
+{
+	/* the protocol of a tensor-core kernel's wait, reduced to its skeleton: a barrier that never completes */
+	__global__ void kernel_bounded_wait_selftest(long long limitCycles, int *deviceStatus)
+	{
+		__shared__ __align__(8) uint64_t never_signalled;
+		__shared__ int abort_flag;
+		if (threadIdx.x == 0)
+		{
+			abort_flag = 0;
+			umma::mbar_init(&never_signalled, 1);
+			umma::mbar_fence_init();
+		}
+		__syncthreads();
+		if (threadIdx.x == 0)
+		{
+			if (not umma::mbar_wait(&never_signalled, 0, &abort_flag, limitCycles))
+				umma::raise_error(&abort_flag, deviceStatus, umma::kErrorSelfTest);
+		}
+		__syncthreads();
+	}
+}
+
+namespace avocado
+{
+	namespace backend
+	{
+		avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, int limitMicroseconds)
+		{
+			if (limitMicroseconds < 1 or limitMicroseconds > 1000000)
+				return AVOCADO_STATUS_BAD_PARAM;
+			AVOCADO_API_BEGIN
+				ContextObject &ctx = getContext(context);
+				ctx.setDevice();
+				int khz = 0;
+				cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx.device);
+				const long long cycles = static_cast<long long>(limitMicroseconds) * std::max(khz, 1000) / 1000;
+				kernel_bounded_wait_selftest<<<1, 32, 0, ctx.getStream()>>>(cycles, ctx.getDeviceStatus());
+				return checkForErrors();
+			AVOCADO_API_END
 		}
 	}
 }

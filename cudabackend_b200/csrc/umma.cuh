@@ -24,7 +24,7 @@ namespace umma
 
 	enum DeviceError
 	{
-		kErrorNone = 0, kErrorTmaWait = 1, kErrorMmaWait = 2, kErrorEpilogueWait = 3, kErrorStageWait = 4
+		kErrorNone = 0, kErrorTmaWait = 1, kErrorMmaWait = 2, kErrorEpilogueWait = 3, kErrorStageWait = 4, kErrorSelfTest = 5
 	};
 
 	__device__ __forceinline__ uint32_t smem_u32(const void *ptr)
@@ -64,7 +64,7 @@ namespace umma
 	}
 	/* Waits for the phase with the given parity to complete.  Returns false when the limit ran out or when
 	 * another role of the CTA has raised *abortFlag (a shared-memory word) because its own wait ran out. */
-	__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abortFlag)
+	__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abortFlag, long long limitCycles = kWaitLimitCycles)
 	{
 		if (mbar_try_wait(bar, parity))
 			return true;
@@ -75,7 +75,7 @@ namespace umma
 			for (int i = 0; i < 64; i++)
 				if (mbar_try_wait(bar, parity))
 					return true;
-			if (*abortFlag != 0 or clock64() - start > kWaitLimitCycles)
+			if (*abortFlag != 0 or clock64() - start > limitCycles)
 				return false;
 		}
 	}
@@ -254,6 +254,77 @@ namespace umma
 				: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
 				"=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
 				: "r"(taddr) : "memory");
+	}
+
+	/* ---- CTA pairs (clusters of two) ---------------------------------------------------------------------
+	 * A pair of CTAs on neighbouring SMs can issue one tcgen05.mma over both SMs' shared memory and TMEM
+	 * (cta_group::2): each CTA supplies half of the rows of A and half of the rows of B, and receives its half of
+	 * the accumulator rows.  The helpers below are what such a kernel needs on top of the single-CTA ones.  Only
+	 * the commit is multicast (an mbarrier arrival at the same offset in both CTAs); no load is. */
+	__device__ __forceinline__ uint32_t cluster_cta_rank()
+	{
+		uint32_t rank;
+		asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+		return rank;
+	}
+	/* shared::cluster address of the given shared::cta address in the CTA of the given rank */
+	__device__ __forceinline__ uint32_t map_to_cta(uint32_t smemAddr, uint32_t rank)
+	{
+		uint32_t result;
+		asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(result) : "r"(smemAddr), "r"(rank));
+		return result;
+	}
+	/* all threads of all CTAs of the cluster */
+	__device__ __forceinline__ void cluster_sync_all()
+	{
+		asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+	}
+	__device__ __forceinline__ void mbar_arrive_cluster(uint32_t clusterAddr)
+	{
+		asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+	}
+	/* loads into THIS CTA's shared memory whose byte count is reported to an mbarrier of either CTA of the pair */
+	__device__ __forceinline__ void tma_load_2d_pair(void *smemDst, const CUtensorMap *map, uint32_t barClusterAddr, int c0, int c1)
+	{
+		asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4}], [%2];"
+				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c0), "r"(c1) : "memory");
+	}
+	__device__ __forceinline__ void tma_load_im2col_4d_pair(void *smemDst, const CUtensorMap *map, uint32_t barClusterAddr, int c, int w, int h, int n,
+			uint16_t offW, uint16_t offH)
+	{
+		asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c), "r"(w), "r"(h), "r"(n), "h"(offW), "h"(offH)
+				: "memory");
+	}
+	/* the same warp index of BOTH CTAs calls these; *smemResult sits at the same offset in both */
+	__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smemResult, uint32_t columns)
+	{
+		asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smemResult)), "r"(columns) : "memory");
+	}
+	__device__ __forceinline__ void tmem_relinquish_pair()
+	{
+		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+	}
+	__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns)
+	{
+		asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+	}
+	/* issued by ONE thread of the pair's first CTA; descriptors hold offsets that are valid in both CTAs */
+	__device__ __forceinline__ void mma_f16_pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, bool accumulate)
+	{
+		asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+				::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate ? 1u : 0u) : "memory");
+	}
+	__device__ __forceinline__ void mma_i8_pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, bool accumulate)
+	{
+		asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+				::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate ? 1u : 0u) : "memory");
+	}
+	/* one arrival on the mbarrier at this offset in every CTA named by the mask, once all MMAs issued so far are done */
+	__device__ __forceinline__ void mma_commit_pair(uint64_t *bar, uint16_t ctaMask)
+	{
+		asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+				::"r"(smem_u32(bar)), "h"(ctaMask) : "memory");
 	}
 
 	/* ---- host side: tensor maps ------------------------------------------------------------------------- */

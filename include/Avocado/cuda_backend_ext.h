@@ -39,6 +39,13 @@ DLL_PUBLIC avStatus_t cudaGetContextStream(avContextDescriptor_t context, void *
  * whose kernels have no device-side waits. */
 DLL_PUBLIC avStatus_t cudaGetLastDeviceStatus(avContextDescriptor_t context, int *result);
 
+/* Failure-detection self test: launches one small kernel that waits, with a limit of `limitMicroseconds`, on a barrier
+ * nobody will ever signal.  The wait must run out, the kernel must return normally, bit 5 of the context's device status
+ * word must be set (read it with cudaGetLastDeviceStatus) and the context must stay usable.  This exercises, without
+ * faulting or hanging the GPU, the path every tensor-core kernel takes when one of its waits gives up.
+ * No counterpart in the reference. */
+DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, int limitMicroseconds);
+
 /* Records the work that API calls enqueue on a context instead of running it, and replays it later with one launch.
  * Between Begin and End every call on `context` is captured into a CUDA graph; host scalars (alpha, beta) are read at
  * capture time and baked in; the memory handles used must stay alive while the graph exists.  Run the same call

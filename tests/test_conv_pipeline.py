@@ -166,9 +166,10 @@ def test_int8_round_half_to_even(ctx):
     assert got.tolist() == expect.tolist() == [0, 2, 2, 0, -2, 64, -64, 4, 4, 6, -2, -4, 1, 2, 0, 6]
 
 
-@pytest.mark.parametrize("shape", [(8, 14, 14, 128, 64), (3, 20, 17, 256, 96), (16, 7, 9, 384, 272)])
+@pytest.mark.parametrize("shape", [(8, 14, 14, 128, 64), (3, 20, 17, 256, 96), (16, 7, 9, 384, 272), (32, 28, 28, 128, 256)])
 def test_int8_tensor_core_shapes(ctx, shape):
-    """shapes that take the tcgen05 kernel: ragged pixel counts, K below / between / above the column-block sizes"""
+    """shapes that take the tcgen05 kernel: ragged pixel counts, K below / between / above the column-block sizes,
+    and more 256-filter tiles than CTA pairs (every pair walks several tiles)"""
     n, h, w, c, k = shape
     got, ref = int8_case(ctx, n, h, w, c, k, (5e-5, 2e-4), activation="relu", with_z=True)
     assert np.array_equal(got, ref)
@@ -199,3 +200,42 @@ def test_implicit_gemm_tensor_core_16bit(ctx, dtype, shape):
     ref = o.conv2d_forward(x, wt, bias=b, z=z, y=y0, alpha1=f(1.1), alpha2=f(1.2), beta=f(0.1), activation="relu")
     # float32 accumulation: the error is the rounding of the stored result
     assert o.error_metrics(got, ref)["elem"] <= {"float16": 1.5e-3, "bfloat16": 1e-2}[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("activation", ["linear", "relu", "tanh"])
+def test_implicit_gemm_tensor_core_16bit_bias_only(ctx, dtype, activation):
+    """without z and beta the kernel takes its short epilogue (linear, relu) or the general one (tanh)"""
+    n, h, w, c, k = 4, 28, 28, 64, 72
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, dtype)
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+    b = d.set_bias(common.uniform("b", (k,), -0.1, 0.1))
+    d.implicit_gemm(alpha1=0.9, activation=activation)
+    ref = o.conv2d_forward(x, wt, bias=b, alpha1=float(np.float32(0.9)), activation=activation)
+    assert o.error_metrics(d.y.download(ctx), ref)["elem"] <= {"float16": 1.5e-3, "bfloat16": 1e-2}[dtype]
+
+
+def test_int8_short_and_general_epilogue_agree(ctx):
+    """alpha1 != 1 and a transcendental activation take the general epilogue; both stay bit-exact against the oracle"""
+    n, h, w, c, k = 8, 14, 14, 128, 64
+    for alpha1, activation in ((None, "relu"), (0.75, "relu"), (None, "sigmoid")):
+        d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "int8")
+        x = common.int8_uniform("x", (n, h, w, c))
+        wt = common.int8_uniform("w", (k, 3, 3, c))
+        bias = common.rng("b").integers(-1000, 1001, k, dtype=np.int32)
+        scales = common.rng("scales").uniform(5e-5, 2e-4, k).astype(np.float32)
+        z = common.int8_uniform("z", (n, h, w, k))
+        d.x.upload(ctx, x)
+        d.wt.upload(ctx, wt)
+        d.set_bias(bias)
+        d.set_scales(scales)
+        d.set_z(z)
+        d.implicit_gemm(alpha1=alpha1, alpha2=0.5, activation=activation)
+        got = d.y.download_raw(ctx)
+        ref = o.conv2d_forward_int8(x, wt, bias, scales, z, alpha1=1.0 if alpha1 is None else alpha1, alpha2=0.5, activation=activation)
+        if activation == "sigmoid":
+            # expf on the device and exp in the oracle may differ by an ulp, which can move a value across a rounding boundary
+            assert np.max(np.abs(got.astype(np.int32) - ref.astype(np.int32))) <= 1
+        else:
+            assert np.array_equal(got, ref), (alpha1, activation)
