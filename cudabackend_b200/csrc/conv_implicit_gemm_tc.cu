@@ -431,12 +431,10 @@ namespace
 					const int rem = m0 - n * image;
 					const int oh = rem / p.out_w;
 					const int ow = rem - oh * p.out_w;
+					/* counters instead of divisions: this single thread's instruction latency is part of every stage's cost */
+					int r = 0, s = 0, cb = 0, tap = 0;
 					for (int kb = 0; kb < p.k_blocks; kb++)
 					{
-						const int tap = kb / p.c_blocks;
-						const int cb = kb - tap * p.c_blocks;
-						const int r = tap / p.kernel_w;
-						const int s = tap - r * p.kernel_w;
 						const int wtap = p.rotate ? (taps - 1 - tap) : tap;
 						if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
 						{
@@ -455,6 +453,16 @@ namespace
 							stage = 0;
 							phase ^= 1u;
 						}
+						if (++cb == p.c_blocks)
+						{
+							cb = 0;
+							tap++;
+							if (++s == p.kernel_w)
+							{
+								s = 0;
+								r++;
+							}
+						}
 					}
 				}
 			}
@@ -464,6 +472,8 @@ namespace
 			if (lane == 0)
 			{
 				constexpr uint32_t idesc = umma::make_instr_desc(Element<T>::kAccum, Element<T>::kFormat, Element<T>::kFormat, false, false, kBlockM, BLOCK_N);
+				/* the descriptor's address field counts 16-byte units: the descriptor of a later stage is this one plus a constant */
+				const uint64_t a_desc0 = umma::make_smem_desc(umma::smem_u32(smem), 16, 1024, umma::kSwizzle128B);
 				int stage = 0;
 				uint32_t phase = 0;
 				int it = 0;
@@ -488,19 +498,14 @@ namespace
 							break;
 						}
 						umma::tcgen05_fence_after();
-						const uint32_t a_addr = umma::smem_u32(smem + stage * Cfg::kStageBytes);
-						const uint32_t b_addr = a_addr + Cfg::kABytes;
-						const uint64_t a_desc = umma::make_smem_desc(a_addr, 16, 1024, umma::kSwizzle128B);
-						const uint64_t b_desc = umma::make_smem_desc(b_addr, 16, 1024, umma::kSwizzle128B);
-#pragma unroll
-						for (int k = 0; k < kElemsPerBlock / kMmaK; k++)
-						{
-							/* one MMA consumes 32 bytes of every row: +2 in descriptor units */
-							if constexpr (Element<T>::kInteger)
-								umma::mma_i8(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
-							else
-								umma::mma_f16(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
-						}
+						const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (Cfg::kStageBytes / 16));
+						const uint64_t b_desc = a_desc + Cfg::kABytes / 16;
+						/* four MMAs, each consuming 32 bytes of every row of the 128-byte-wide stage */
+						static_assert(kElemsPerBlock / kMmaK == 4, "a stage is four MMAs deep");
+						if constexpr (Element<T>::kInteger)
+							umma::mma_i8_k4(tmem_d, a_desc, b_desc, idesc, kb != 0);
+						else
+							umma::mma_f16_k4(tmem_d, a_desc, b_desc, idesc, kb != 0);
 						umma::mma_commit(&empty_bar[stage]);
 						if (++stage == STAGES)
 						{
@@ -697,12 +702,9 @@ namespace
 					const int rem = m0 - n * image;
 					const int oh = rem / p.out_w;
 					const int ow = rem - oh * p.out_w;
+					int r = 0, s = 0, cb = 0, tap = 0;
 					for (int kb = 0; kb < p.k_blocks; kb++)
 					{
-						const int tap = kb / p.c_blocks;
-						const int cb = kb - tap * p.c_blocks;
-						const int r = tap / p.kernel_w;
-						const int s = tap - r * p.kernel_w;
 						const int wtap = p.rotate ? (taps - 1 - tap) : tap;
 						if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
 						{
@@ -723,6 +725,16 @@ namespace
 						{
 							stage = 0;
 							phase ^= 1u;
+						}
+						if (++cb == p.c_blocks)
+						{
+							cb = 0;
+							tap++;
+							if (++s == p.kernel_w)
+							{
+								s = 0;
+								r++;
+							}
 						}
 					}
 				}

@@ -19,6 +19,13 @@ namespace bk
 	/* fused Winograd F(2x2,3x3) forward on tcgen05 */
 	avocado::backend::avStatus_t launch_winograd_fused_tc(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
 			avocado::backend::avDataType_t xType, avocado::backend::avDataType_t yType, const void *alpha1, const void *alpha2, const void *beta);
+
+	/* Contraction + output transform of the F(2x2,3x3) convolution in one kernel: reads V[16][tiles][C] and U[16][K][C]
+	 * (float16), writes y (float16 / bfloat16) with the bias / z / activation / beta epilogue of args.  deviceStatus is
+	 * the word that receives the bit of a wait that ran out. */
+	avocado::backend::avStatus_t winograd_f23_contract_output(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
+			avocado::backend::avDataType_t yType, long long tiles, const void *vPtr, const void *uPtr, const void *alpha1, const void *alpha2, const void *beta,
+			int *deviceStatus);
 } /* namespace bk */
 
 #endif /* B200_CONV_KERNELS_HPP_ */

@@ -265,11 +265,14 @@ namespace
 				int stage = 0;
 				uint32_t phase = 0;
 				bool ok = true;
+				/* (plane, row block, column block) of the tile advance by a fixed step: decomposed once, then carried, so that
+				 * this thread executes no division per tile */
+				int nb = static_cast<int>(blockIdx.x) % nBlocks, mb = (static_cast<int>(blockIdx.x) / nBlocks) % mBlocks,
+						p = static_cast<int>(blockIdx.x) / (nBlocks * mBlocks);
+				const int step_nb = static_cast<int>(gridDim.x) % nBlocks, step_mb = (static_cast<int>(gridDim.x) / nBlocks) % mBlocks,
+						step_p = static_cast<int>(gridDim.x) / (nBlocks * mBlocks);
 				for (int tile = blockIdx.x; tile < numTiles and ok; tile += gridDim.x)
 				{
-					const int nb = tile % nBlocks;
-					const int mb = (tile / nBlocks) % mBlocks;
-					const int p = tile / (nBlocks * mBlocks);
 					for (int kb = 0; kb < kBlocks; kb++)
 					{
 						if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
@@ -288,6 +291,19 @@ namespace
 							stage = 0;
 							phase ^= 1u;
 						}
+					}
+					nb += step_nb;
+					mb += step_mb;
+					p += step_p;
+					if (nb >= nBlocks)
+					{
+						nb -= nBlocks;
+						mb++;
+					}
+					if (mb >= mBlocks)
+					{
+						mb -= mBlocks;
+						p++;
 					}
 				}
 			}

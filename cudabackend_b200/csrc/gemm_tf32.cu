@@ -45,11 +45,12 @@ namespace
 			static constexpr int kTmemColumns = 2 * BLOCK_N;
 	};
 
+	/* x rounded to TF32 (10 explicit mantissa bits), ties away from zero like cvt.rna.tf32.f32, with two integer
+	 * operations: the conversion instruction runs on the slow conversion pipe, and the splitter warps execute it for
+	 * every operand element, which made them the pace-setter of the whole kernel. */
 	__device__ __forceinline__ uint32_t to_tf32(float x)
 	{
-		uint32_t r;
-		asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-		return r;
+		return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u;
 	}
 	/* hi = x rounded to TF32, lo = (x - hi) rounded to TF32; x - hi is exact in float32 */
 	__device__ __forceinline__ void split4(uint4 raw, uint4 &hi, uint4 &lo)
@@ -126,11 +127,14 @@ namespace
 				int stage = 0;
 				uint32_t phase = 0;
 				bool ok = true;
+				/* (plane, row block, column block) of the tile advance by a fixed step: decomposed once, then carried, so that
+				 * this thread executes no division per tile */
+				int nb = static_cast<int>(blockIdx.x) % nBlocks, mb = (static_cast<int>(blockIdx.x) / nBlocks) % mBlocks,
+						p = static_cast<int>(blockIdx.x) / (nBlocks * mBlocks);
+				const int step_nb = static_cast<int>(gridDim.x) % nBlocks, step_mb = (static_cast<int>(gridDim.x) / nBlocks) % mBlocks,
+						step_p = static_cast<int>(gridDim.x) / (nBlocks * mBlocks);
 				for (int tile = blockIdx.x; tile < numTiles and ok; tile += gridDim.x)
 				{
-					const int nb = tile % nBlocks;
-					const int mb = (tile / nBlocks) % mBlocks;
-					const int p = tile / (nBlocks * mBlocks);
 					for (int kb = 0; kb < kBlocks; kb++)
 					{
 						if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
@@ -148,6 +152,19 @@ namespace
 							stage = 0;
 							phase ^= 1u;
 						}
+					}
+					nb += step_nb;
+					mb += step_mb;
+					p += step_p;
+					if (nb >= nBlocks)
+					{
+						nb -= nBlocks;
+						mb++;
+					}
+					if (mb >= mBlocks)
+					{
+						mb -= mBlocks;
+						p++;
 					}
 				}
 			}

@@ -226,6 +226,25 @@ namespace umma
 		asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
 				::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate ? 1u : 0u) : "memory");
 	}
+	/* Four MMAs over one 128-byte-wide K-major stage (descriptor + 0, 2, 4, 6 = 32-byte steps along the contraction) in
+	 * one instruction sequence.  The issuing thread is a single thread whose own instruction latency adds to every MMA it
+	 * issues; with short MMAs (N <= 128 takes 64 cycles or less) that latency, not the tensor pipe, sets the pace, so the
+	 * per-MMA predicate set-up and descriptor arithmetic of the single-MMA wrappers is folded here. */
+#define B200_UMMA_K4(NAME, KIND) \
+	__device__ __forceinline__ void NAME(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, bool accumulateFirst) \
+	{ \
+		asm volatile("{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t" \
+				"setp.ne.b32 p, %4, 0;\n\tsetp.eq.u32 q, %3, %3;\n\t" \
+				"add.s64 a1, %1, 2;\n\tadd.s64 b1, %2, 2;\n\tadd.s64 a2, %1, 4;\n\tadd.s64 b2, %2, 4;\n\tadd.s64 a3, %1, 6;\n\tadd.s64 b3, %2, 6;\n\t" \
+				"tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %2, %3, p;\n\t" \
+				"tcgen05.mma.cta_group::1.kind::" KIND " [%0], a1, b1, %3, q;\n\t" \
+				"tcgen05.mma.cta_group::1.kind::" KIND " [%0], a2, b2, %3, q;\n\t" \
+				"tcgen05.mma.cta_group::1.kind::" KIND " [%0], a3, b3, %3, q;\n\t}" \
+				::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulateFirst ? 1u : 0u) : "memory"); \
+	}
+	B200_UMMA_K4(mma_f16_k4, "f16")
+	B200_UMMA_K4(mma_i8_k4, "i8")
+#undef B200_UMMA_K4
 	/* makes the mbarrier track completion of all MMAs issued so far by this thread (one arrival) */
 	__device__ __forceinline__ void mma_commit(uint64_t *bar)
 	{

@@ -29,6 +29,7 @@
 
 #include "objects.hpp"
 #include "winograd_internal.hpp"
+#include "conv_kernels.hpp"
 
 #include <mutex>
 
@@ -153,6 +154,16 @@ namespace avocado
 				status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr, status_word);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;
+				{
+					/* the same single-kernel contraction + output transform the allocating entry point uses */
+					bk::ConvArgs args = { };
+					args.batch = batch, args.height = height, args.width = width, args.channels = channels, args.filters = filters;
+					args.out_height = height, args.out_width = width;
+					args.y = yPtr, args.bias = bPtr, args.z = zPtr, args.activation = activation;
+					status = bk::winograd_f23_contract_output(ctx, args, y.dtype, tiles, v_ptr, u_ptr, alpha1, alpha2, beta, status_word);
+					if (status != AVOCADO_STATUS_NOT_SUPPORTED)
+						return status;
+				}
 				status = bk::gemm_batched_nt_tensor_core(ctx, v, v_ptr, u, u_ptr, m, m_ptr, status_word);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;

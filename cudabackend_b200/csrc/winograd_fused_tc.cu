@@ -9,7 +9,8 @@
  *
  *   U = weight transform(w)        V = input transform(x)        M = V x U^T (tcgen05)        y = output transform(M)
  *
- * with the bias / z / activation / beta epilogue fused into the output transform.  The transform-domain tensors are
+ * with the bias / z / activation / beta epilogue fused into the output transform.  For float16 / bfloat16 tensors the
+ * last two steps are ONE kernel (winograd_fused_f23_tc.cu): M stays in TMEM and is never written to memory.  The transform-domain tensors are
  * internal, so their format is chosen for accuracy: float16 for float16 AND bfloat16 tensors with F(2x2,3x3) (a
  * bfloat16 domain would miss 1e-2, F(4x4,3x3) needs more than 10 mantissa bits), float32 with F(4x4,3x3) for float32.
  * The scratch buffer belongs to the context, grows on demand and is reused by the next call on that context, so
@@ -31,6 +32,16 @@ namespace bk
 		size_t align_up(size_t value, size_t alignment)
 		{
 			return (value + alignment - 1) / alignment * alignment;
+		}
+		/* AVOCADO_B200_WINOGRAD=chained keeps the batched GEMM and the output transform as two kernels (A/B comparison) */
+		bool chained_form_forced()
+		{
+			static const bool forced = []()
+			{
+				const char *env = std::getenv("AVOCADO_B200_WINOGRAD");
+				return env != nullptr and std::strcmp(env, "chained") == 0;
+			}();
+			return forced;
 		}
 		TensorObject make_tensor(avDataType_t dtype, std::initializer_list<int> dims)
 		{
@@ -105,6 +116,13 @@ namespace bk
 		status = winograd_input_transform(ctx, conv, transform_size, w, x, args.x, v, v_ptr);
 		if (status != AVOCADO_STATUS_SUCCESS)
 			return status;
+		if (transform_size == 2 and not chained_form_forced())
+		{
+			/* contraction and output transform in one kernel; M is never written */
+			status = winograd_f23_contract_output(ctx, args, yType, tiles, v_ptr, u_ptr, alpha1, alpha2, beta, ctx.getDeviceStatus());
+			if (status != AVOCADO_STATUS_NOT_SUPPORTED)
+				return status;
+		}
 		status = gemm_batched(ctx, false, true, nullptr, v, v_ptr, u, u_ptr, nullptr, m, m_ptr);
 		if (status != AVOCADO_STATUS_SUCCESS)
 			return status;
