@@ -227,7 +227,9 @@ class Workload:
         self.host_y = None
 
     def launches_per_step(self):
-        return {"winograd_nonfused": 4, "training": 4 + 4 + 4, "winograd_fused": 2, "implicit_gemm": 1}[self.cfg["kind"]]
+        # kernels of this library launched per step: forward chain 4; dX chain 5 (its (N,N) contraction transposes U first);
+        # dW chain 5 (split contraction + fixed-order reduction); one-call Winograd 3 (weight, input, contraction + output)
+        return {"winograd_nonfused": 4, "training": 4 + 5 + 5, "winograd_fused": 3, "implicit_gemm": 1}[self.cfg["kind"]]
 
     def stages(self):
         """(name, callable) pairs making up one step, in issue order."""
@@ -498,6 +500,30 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         line["stage_hbm_frac"] = {name: line["stage_gbs"][name] / peaks["hbm_gbs"] for name in stage_names}
         total_bytes = sum(sb[name] for name in stage_names)
         line["pipeline_hbm_frac"] = total_bytes / (elapsed_ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]
+    elif cfg["kind"] in ("winograd_fused", "training"):
+        # pipelines of HBM-bound kernels: the bytes every kernel of the step must move (inputs read once, outputs written
+        # once, transform-domain tensors written by one kernel and read by the next), against the measured copy bandwidth
+        n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
+        b = elem_size(cfg["dtype"])
+        step_s = elapsed_ms / args.steps * 1e-3
+        if cfg["kind"] == "winograd_fused":
+            t = n * ((h + 1) // 2) * ((w + 1) // 2)
+            u = 16 * k * c * 2
+            algorithmic = (9 * k * c * b + u) + (n * h * w * c * b + 16 * t * c * 2) + (16 * t * c * 2 + u + n * h * w * k * b)
+            kernels = "weight transform, input transform, kernel_f23_contract_output (contraction + output transform; M stays in TMEM)"
+        else:
+            t = n * ((h + 3) // 4) * ((w + 3) // 4)
+            m = 4
+            u = 36 * k * c * m
+            transform_in = n * h * w * c * b + 36 * t * c * m
+            transform_out = 36 * t * k * m + n * h * w * k * b
+            gemm = 36 * t * (c + k) * m + u
+            algorithmic = (transform_in + gemm + transform_out) * 2 + (transform_in + transform_out + gemm) + 3 * (9 * k * c * b + u)
+            kernels = "12 kernels: forward, dX and dW chains (transforms + 3xTF32 tcgen05 contractions)"
+        achieved = algorithmic / step_s / 1e9
+        line["roofline"] = {"kernel": kernels, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": achieved / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": algorithmic, "peak_source": peaks["source"],
+                            "tensor_tflops_effective": flops / step_s / 1e12}
     else:
         n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
         b = elem_size(cfg["dtype"])

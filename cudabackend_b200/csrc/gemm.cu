@@ -314,6 +314,7 @@ namespace
 			{
 				constexpr uint32_t idesc = umma::make_instr_desc(umma::kAccumF32, IS_BF16 ? umma::kFormatBF16 : umma::kFormatF16,
 						IS_BF16 ? umma::kFormatBF16 : umma::kFormatF16, false, false, kBlockM, BLOCK_N);
+				const uint64_t a_desc0 = umma::make_smem_desc(umma::smem_u32(smem), 16, 1024, umma::kSwizzle128B);
 				int stage = 0;
 				uint32_t phase = 0;
 				int it = 0;
@@ -338,16 +339,11 @@ namespace
 							break;
 						}
 						umma::tcgen05_fence_after();
-						const uint32_t a_addr = umma::smem_u32(smem + stage * Cfg::kStageBytes);
-						const uint32_t b_addr = a_addr + Cfg::kABytes;
-						const uint64_t a_desc = umma::make_smem_desc(a_addr, 16, 1024, umma::kSwizzle128B);
-						const uint64_t b_desc = umma::make_smem_desc(b_addr, 16, 1024, umma::kSwizzle128B);
-#pragma unroll
-						for (int k = 0; k < kBlockK / 16; k++)
-						{
-							/* advancing 16 elements = 32 bytes inside the 128-byte swizzle row: +2 in descriptor units */
-							umma::mma_f16(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
-						}
+						/* the descriptor's address field counts 16-byte units; four MMAs of 16 elements (32 bytes of the
+						 * 128-byte swizzle row each) consume the stage */
+						static_assert(kBlockK / 16 == 4, "a stage is four MMAs deep");
+						const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (Cfg::kStageBytes / 16));
+						umma::mma_f16_k4(tmem_d, a_desc, a_desc + Cfg::kABytes / 16, idesc, kb != 0);
 						umma::mma_commit(&empty_bar[stage]);
 						if (++stage == STAGES)
 						{
