@@ -390,11 +390,35 @@ namespace
 	constexpr int kTnBBlocks = kTnBlockN / 32;
 	/* per stage: A hi (4 blocks), A lo, B hi (2 blocks), B lo */
 	constexpr int kTnStageBytes = 2 * kTnABlocks * kTnBlockBytes + 2 * kTnBBlocks * kTnBlockBytes;
-	constexpr int kTnSmemBytes = kTnStages * kTnStageBytes + 1024;
 
+	/* Two batch entries per MMA.  When the result has at most 64 rows and 64 columns (the dW product of a 64-channel
+	 * layer), half of the 128 accumulator rows of the form above would be padding, and an MMA with N = 64 occupies the
+	 * tensor pipe as long as one with N = 128.  The paired form stacks entries 2q and 2q+1: rows 0..63 / 64..127 of A and
+	 * columns 0..63 / 64..127 of B come from the two entries, so the two diagonal 64 x 64 blocks of the 128 x 128
+	 * accumulator are the two results (the off-diagonal blocks are products of unrelated operands and are dropped).
+	 * Every byte of a stage is then real data: twice the bytes in flight and half the MMAs per byte. */
+	template<bool PAIR>
+	struct TnLayout
+	{
+			static constexpr int kABlocks = 4;
+			static constexpr int kBBlocks = PAIR ? 4 : 2;
+			static constexpr int kBlockN = PAIR ? 128 : 64;
+			static constexpr int kStages = PAIR ? 3 : 4;
+			static constexpr int kALo = kABlocks * kTnBlockBytes;
+			static constexpr int kBHi = 2 * kABlocks * kTnBlockBytes;
+			static constexpr int kBLo = kBHi + kBBlocks * kTnBlockBytes;
+			static constexpr int kStageBytes = 2 * (kABlocks + kBBlocks) * kTnBlockBytes;
+			static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+	};
+
+	template<bool PAIR>
 	__global__ void __launch_bounds__(kThreads, 1) kernel_gemm_tn_tf32x3(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
 			float *__restrict__ partial, int M, int N, int mBlocks, int nBlocks, int kBlocksTotal, int kBlocksPerSplit, int *deviceStatus)
 	{
+		using L = TnLayout<PAIR>;
+		constexpr int kTnStages = L::kStages; /* shadow the unpaired constants inside this kernel */
+		constexpr int kTnStageBytes = L::kStageBytes;
+		constexpr int kTnBlockN = L::kBlockN;
 		extern __shared__ uint8_t smem_raw[];
 		uint8_t *smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 		__shared__ __align__(8) uint64_t full_bar[kTnStages];
@@ -409,14 +433,16 @@ namespace
 		const int lane = threadIdx.x % 32;
 		const int split = blockIdx.x;
 		const int tile = blockIdx.y;
-		const int nb = tile % nBlocks;
-		const int mb = (tile / nBlocks) % mBlocks;
-		const int p = tile / (nBlocks * mBlocks);
+		/* unpaired: tile = (batch entry, row block, column block); paired: tile = pair of batch entries, one block each */
+		const int nb = PAIR ? 0 : tile % nBlocks;
+		const int mb = PAIR ? 0 : (tile / nBlocks) % mBlocks;
+		const int p = PAIR ? 2 * tile : tile / (nBlocks * mBlocks);
 		const int kb_begin = split * kBlocksPerSplit;
 		const int kb_end = min(kBlocksTotal, kb_begin + kBlocksPerSplit);
-		const int m0 = mb * kBlockM, n0 = nb * kTnBlockN;
-		const int a_blocks = min(kTnABlocks, (M - m0 + 31) / 32); /* column blocks of A that hold real data */
-		const int b_blocks = min(kTnBBlocks, (N - n0 + 31) / 32);
+		const int m0 = mb * kBlockM, n0 = nb * 64;
+		/* column blocks (of 32) that hold real data, per batch entry */
+		const int a_blocks = min(PAIR ? 2 : kTnABlocks, (M - m0 + 31) / 32);
+		const int b_blocks = min(2, (N - n0 + 31) / 32);
 
 		/* column blocks that are never loaded must read as zero, in the hi and the lo copy */
 		for (int i = threadIdx.x; i < kTnStages * kTnStageBytes / 16; i += kThreads)
@@ -446,9 +472,9 @@ namespace
 		umma::tcgen05_fence_after();
 		const uint32_t tmem_base = tmem_base_slot;
 		volatile int *abort_ptr = &abort_flag;
-		constexpr int a_lo_offset = kTnABlocks * kTnBlockBytes;
-		constexpr int b_hi_offset = 2 * kTnABlocks * kTnBlockBytes;
-		constexpr int b_lo_offset = b_hi_offset + kTnBBlocks * kTnBlockBytes;
+		constexpr int a_lo_offset = L::kALo;
+		constexpr int b_hi_offset = L::kBHi;
+		constexpr int b_lo_offset = L::kBLo;
 
 		if (warp == 0)
 		{
@@ -464,11 +490,19 @@ namespace
 						break;
 					}
 					uint8_t *base = smem + stage * kTnStageBytes;
-					umma::mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>((a_blocks + b_blocks) * kTnBlockBytes));
+					umma::mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>((PAIR ? 2 : 1) * (a_blocks + b_blocks) * kTnBlockBytes));
 					for (int b = 0; b < a_blocks; b++)
 						umma::tma_load_3d(base + b * kTnBlockBytes, &mapA, &full_bar[stage], m0 + 32 * b, kb * kBlockK, p);
 					for (int b = 0; b < b_blocks; b++)
 						umma::tma_load_3d(base + b_hi_offset + b * kTnBlockBytes, &mapB, &full_bar[stage], n0 + 32 * b, kb * kBlockK, p);
+					if (PAIR)
+					{
+						/* the second entry of the pair fills the upper half of the rows of A and of the columns of B */
+						for (int b = 0; b < a_blocks; b++)
+							umma::tma_load_3d(base + (2 + b) * kTnBlockBytes, &mapA, &full_bar[stage], 32 * b, kb * kBlockK, p + 1);
+						for (int b = 0; b < b_blocks; b++)
+							umma::tma_load_3d(base + b_hi_offset + (2 + b) * kTnBlockBytes, &mapB, &full_bar[stage], 32 * b, kb * kBlockK, p + 1);
+					}
 					if (++stage == kTnStages)
 					{
 						stage = 0;
@@ -524,8 +558,10 @@ namespace
 			const int split_thread = threadIdx.x - 64;
 			int stage = 0;
 			uint32_t phase = 0;
-			const int a_chunks = a_blocks * kTnBlockBytes / 16;
-			const int b_chunks = b_blocks * kTnBlockBytes / 16;
+			/* paired: the second entry's blocks start at block 2, so the split covers blocks 0 .. 2 + count - 1 (a block in
+			 * between that was never loaded holds zeros and splits into zeros) */
+			const int a_chunks = (PAIR ? 2 + a_blocks : a_blocks) * kTnBlockBytes / 16;
+			const int b_chunks = (PAIR ? 2 + b_blocks : b_blocks) * kTnBlockBytes / 16;
 			for (int kb = kb_begin; kb < kb_end; kb++)
 			{
 				if (split_thread == 0)
@@ -580,12 +616,19 @@ namespace
 			if (has_work and not ready and lane == 0)
 				umma::raise_error(abort_ptr, deviceStatus, umma::kErrorEpilogueWait);
 			umma::tcgen05_fence_after();
-			float *dst = partial + ((static_cast<size_t>(split) * gridDim.y + tile) * kBlockM + row) * kTnBlockN;
+			/* partial tiles are stored per batch entry as 128 rows x 64 columns whatever the form; in the paired form rows
+			 * 0..63 hold entry 2q (accumulator columns 0..63) and rows 64..127 entry 2q+1 (columns 64..127), each written
+			 * to rows 0..63 of its own entry's tile */
+			const int entry_tile = PAIR ? 2 * tile + (row >= 64 ? 1 : 0) : tile;
+			const int entry_tiles = PAIR ? 2 * static_cast<int>(gridDim.y) : static_cast<int>(gridDim.y);
+			const int entry_row = PAIR ? (row & 63) : row;
+			const int first_column = (PAIR and row >= 64) ? 64 : 0;
+			float *dst = partial + ((static_cast<size_t>(split) * entry_tiles + entry_tile) * kBlockM + entry_row) * 64;
 #pragma unroll
-			for (int chunk = 0; chunk < kTnBlockN / 32; chunk++)
+			for (int chunk = 0; chunk < 2; chunk++)
 			{
 				uint32_t r[32];
-				umma::tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(chunk * 32), r);
+				umma::tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(first_column + chunk * 32), r);
 				umma::tmem_load_wait();
 #pragma unroll
 				for (int j = 0; j < 8; j++)
@@ -662,8 +705,11 @@ namespace
 		const int kBlocks = (s.Kc + kBlockK - 1) / kBlockK;
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
+		/* results of at most 64 x 64 are computed two batch entries at a time */
+		const bool paired = s.M <= 64 and s.N <= 64 and s.batch >= 2 and s.batch % 2 == 0;
+		const long long grid_tiles = paired ? tiles / 2 : tiles;
 		/* as many splits as fit two CTAs' worth of work per SM, but at least 8 contraction blocks per split */
-		int splits = static_cast<int>(std::max<long long>(1, std::min<long long>((2 * sms) / tiles, (kBlocks + 7) / 8)));
+		int splits = static_cast<int>(std::max<long long>(1, std::min<long long>((2 * sms) / grid_tiles, (kBlocks + 7) / 8)));
 		const int kBlocksPerSplit = (kBlocks + splits - 1) / splits;
 		splits = (kBlocks + kBlocksPerSplit - 1) / kBlocksPerSplit;
 		const size_t partial_bytes = static_cast<size_t>(splits) * tiles * kBlockM * kTnBlockN * sizeof(float);
@@ -672,13 +718,18 @@ namespace
 		static bool configured[kMaxDevices] = { };
 		if (not configured[ctx.device])
 		{
-			if (cudaFuncSetAttribute(kernel_gemm_tn_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmemBytes) != cudaSuccess)
+			if (cudaFuncSetAttribute(kernel_gemm_tn_tf32x3<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TnLayout<false>::kSmemBytes) != cudaSuccess
+					or cudaFuncSetAttribute(kernel_gemm_tn_tf32x3<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TnLayout<true>::kSmemBytes) != cudaSuccess)
 				return checkForErrors();
 			configured[ctx.device] = true;
 		}
-		const dim3 grid(splits, static_cast<unsigned int>(tiles));
-		kernel_gemm_tn_tf32x3<<<grid, kThreads, kTnSmemBytes, ctx.getStream()>>>(mapA, mapB, partial, s.M, s.N, mBlocks, nBlocks, kBlocks, kBlocksPerSplit,
-				ctx.getDeviceStatus());
+		const dim3 grid(splits, static_cast<unsigned int>(grid_tiles));
+		if (paired)
+			kernel_gemm_tn_tf32x3<true> <<<grid, kThreads, TnLayout<true>::kSmemBytes, ctx.getStream()>>>(mapA, mapB, partial, s.M, s.N, mBlocks, nBlocks, kBlocks,
+					kBlocksPerSplit, ctx.getDeviceStatus());
+		else
+			kernel_gemm_tn_tf32x3<false> <<<grid, kThreads, TnLayout<false>::kSmemBytes, ctx.getStream()>>>(mapA, mapB, partial, s.M, s.N, mBlocks, nBlocks, kBlocks,
+					kBlocksPerSplit, ctx.getDeviceStatus());
 		avStatus_t status = checkForErrors();
 		if (status != AVOCADO_STATUS_SUCCESS)
 			return status;

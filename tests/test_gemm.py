@@ -125,7 +125,8 @@ def test_gemm_batched_tensor_core_float32(ctx, shape, trans_b):
 
 
 # (batch, contraction length, rows of the result, columns of the result)
-TN_SHAPES = [(36, 392, 64, 64), (36, 6272, 64, 64), (4, 1000, 72, 200), (3, 77, 20, 36), (2, 33, 128, 64), (1, 4096, 256, 136)]
+TN_SHAPES = [(36, 392, 64, 64), (36, 6272, 64, 64), (4, 1000, 72, 200), (3, 77, 20, 36), (2, 33, 128, 64), (1, 4096, 256, 136),
+             (4, 100, 20, 36), (2, 33, 64, 40), (6, 900, 33, 64)]  # the last three: two batch entries per MMA, ragged blocks
 
 
 @pytest.mark.parametrize("shape", TN_SHAPES)
