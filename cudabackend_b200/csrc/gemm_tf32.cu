@@ -85,7 +85,6 @@ namespace
 		__shared__ uint32_t tmem_base_slot;
 		__shared__ int abort_flag;
 		__shared__ volatile int epilogue_go;
-		__shared__ volatile int splitter_go;
 
 		const int warp = threadIdx.x / 32;
 		const int lane = threadIdx.x % 32;
@@ -235,15 +234,17 @@ namespace
 			{
 				for (int kb = 0; kb < kBlocks; kb++)
 				{
-					if (split_thread == 0)
+					/* every warp waits by itself (its first lane polls, the outcome is broadcast): the four warps own fixed
+					 * quarters of the stage, so nothing else has to be agreed between them */
+					int ready = 0;
+					if (lane == 0)
 					{
-						const bool ready = umma::mbar_wait(&full_bar[stage], phase, abort_ptr);
-						if (not ready)
+						ready = umma::mbar_wait(&full_bar[stage], phase, abort_ptr) ? 1 : 0;
+						if (ready == 0)
 							umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
-						splitter_go = ready ? 1 : 0;
 					}
-					umma::named_barrier_sync(2, 128);
-					if (splitter_go == 0)
+					ready = __shfl_sync(0xFFFFFFFFu, ready, 0);
+					if (ready == 0)
 					{
 						ok = false;
 						break;
@@ -271,8 +272,6 @@ namespace
 					}
 					umma::fence_proxy_async_smem();
 					umma::mbar_arrive(&split_bar[stage]);
-					/* all splitters must be past reading splitter_go before thread 0 writes it again */
-					umma::named_barrier_sync(2, 128);
 					if (++stage == STAGES)
 					{
 						stage = 0;
@@ -384,12 +383,9 @@ namespace
 	 * Output rows beyond M inside a 128-row tile come from column blocks that are never loaded and are zeroed once.
 	 * --------------------------------------------------------------------------------------------------------- */
 	constexpr int kTnBlockN = 64;
-	constexpr int kTnStages = 4;
 	constexpr int kTnBlockBytes = 32 * 128; /* one column block: 32 contraction rows x 32 float32 */
 	constexpr int kTnABlocks = kBlockM / 32;
-	constexpr int kTnBBlocks = kTnBlockN / 32;
-	/* per stage: A hi (4 blocks), A lo, B hi (2 blocks), B lo */
-	constexpr int kTnStageBytes = 2 * kTnABlocks * kTnBlockBytes + 2 * kTnBBlocks * kTnBlockBytes;
+	/* per stage: A hi (4 blocks), A lo, B hi (2 or 4 blocks), B lo: see TnLayout */
 
 	/* Two batch entries per MMA.  When the result has at most 64 rows and 64 columns (the dW product of a 64-channel
 	 * layer), half of the 128 accumulator rows of the form above would be padding, and an MMA with N = 64 occupies the
@@ -416,9 +412,9 @@ namespace
 			float *__restrict__ partial, int M, int N, int mBlocks, int nBlocks, int kBlocksTotal, int kBlocksPerSplit, int *deviceStatus)
 	{
 		using L = TnLayout<PAIR>;
-		constexpr int kTnStages = L::kStages; /* shadow the unpaired constants inside this kernel */
+		constexpr int kTnStages = L::kStages;
 		constexpr int kTnStageBytes = L::kStageBytes;
-		constexpr int kTnBlockN = L::kBlockN;
+		constexpr int kTnBlockN = L::kBlockN; /* accumulator columns of this form (the file-scope constant is the 64 of a stored tile) */
 		extern __shared__ uint8_t smem_raw[];
 		uint8_t *smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 		__shared__ __align__(8) uint64_t full_bar[kTnStages];
@@ -427,7 +423,6 @@ namespace
 		__shared__ __align__(8) uint64_t tmem_full_bar;
 		__shared__ uint32_t tmem_base_slot;
 		__shared__ int abort_flag;
-		__shared__ volatile int splitter_go;
 
 		const int warp = threadIdx.x / 32;
 		const int lane = threadIdx.x % 32;
@@ -564,15 +559,15 @@ namespace
 			const int b_chunks = (PAIR ? 2 + b_blocks : b_blocks) * kTnBlockBytes / 16;
 			for (int kb = kb_begin; kb < kb_end; kb++)
 			{
-				if (split_thread == 0)
+				int ready = 0;
+				if (lane == 0)
 				{
-					const bool ready = umma::mbar_wait(&full_bar[stage], phase, abort_ptr);
-					if (not ready)
+					ready = umma::mbar_wait(&full_bar[stage], phase, abort_ptr) ? 1 : 0;
+					if (ready == 0)
 						umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
-					splitter_go = ready ? 1 : 0;
 				}
-				umma::named_barrier_sync(2, 128);
-				if (splitter_go == 0)
+				ready = __shfl_sync(0xFFFFFFFFu, ready, 0);
+				if (ready == 0)
 					break;
 				umma::mbar_try_wait(&full_bar[stage], phase);
 				uint4 *a_hi = reinterpret_cast<uint4*>(smem + stage * kTnStageBytes);
@@ -595,7 +590,6 @@ namespace
 				}
 				umma::fence_proxy_async_smem();
 				umma::mbar_arrive(&split_bar[stage]);
-				umma::named_barrier_sync(2, 128);
 				if (++stage == kTnStages)
 				{
 					stage = 0;
@@ -794,7 +788,7 @@ namespace
 				return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
 		if (blockN == 64)
-			return launch_config<64, 3>(ctx, s, mapA, mapB, mapC, alpha);
+			return launch_config<64, 4>(ctx, s, mapA, mapB, mapC, alpha);
 		return launch_config<128, 2>(ctx, s, mapA, mapB, mapC, alpha);
 	}
 }
