@@ -141,6 +141,7 @@ def elem_size(dtype):
 def cpu_sample(cfg, images):
     """Runs the naive CPU convolution on `images` images of the workload; returns (seconds, flops done)."""
     from oracle import oracle as o
+    o.use_all_host_threads()  # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use the whole host
     sub = dict(cfg, n=images)
     data = synthetic(sub)
     t0 = time.perf_counter()

@@ -69,6 +69,17 @@ static double activate(int activation, double x)
 	}
 }
 
+/* number of threads the OpenMP loops below use from now on (a launcher may have exported OMP_NUM_THREADS=1) */
+void oracle_set_threads(int threads)
+{
+#ifdef _OPENMP
+	if (threads > 0)
+		omp_set_num_threads(threads);
+#else
+	(void) threads;
+#endif
+}
+
 int oracle_max_threads(void)
 {
 #ifdef _OPENMP

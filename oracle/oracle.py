@@ -36,6 +36,13 @@ def max_threads():
     return int(lib().oracle_max_threads())
 
 
+def use_all_host_threads():
+    """Lets the OpenMP loops use every core the process may run on, whatever OMP_NUM_THREADS a launcher exported."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(int(cores))
+    return max_threads()
+
+
 def _p(a, ctype):
     if a is None:
         return ctypes.POINTER(ctype)()
