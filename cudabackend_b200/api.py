@@ -82,6 +82,7 @@ SIGNATURES = {
     "cudaDestroyCapturedGraph": (_INT, [_I64]),
     "cudaConvolutionWinogradFusedForwardNoAlloc": (_INT, _conv_args),
     "cudaRunBoundedWaitSelfTest": (_INT, [_H, _INT]),
+    "cudaIm2Row": (_INT, [_H, _H, _H, _H, _H, _H, _H]),
 }
 
 # exported for link compatibility, return NOT_SUPPORTED
@@ -89,7 +90,7 @@ UNSUPPORTED_SYMBOLS = ["cudaChangeType", "cudaConcatTensors", "cudaSplitTensors"
                        "cudaAddTensors", "cudaAddBias", "cudaBinaryOp", "cudaUnaryOp", "cudaReduceTensor", "cudaActivationForward",
                        "cudaActivationBackward", "cudaSoftmaxForward", "cudaSoftmaxBackward", "cudaAffineForward", "cudaBatchNormInference",
                        "cudaBatchNormForward", "cudaBatchNormBackward", "cudaDropoutForward", "cudaDropoutBackward", "cudaPoolingForward",
-                       "cudaPoolingBackward", "cudaIm2Row", "cudaMetricFunction", "cudaLossFunction", "cudaLossGradient", "cudaOptimizerLearn",
+                       "cudaPoolingBackward", "cudaMetricFunction", "cudaLossFunction", "cudaLossGradient", "cudaOptimizerLearn",
                        "cudaRegularizerL2"]
 
 

@@ -103,10 +103,6 @@ namespace avocado
 		{
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
-		avStatus_t cudaIm2Row(avContextDescriptor_t, const avConvolutionDescriptor_t, const avTensorDescriptor_t, const avTensorDescriptor_t, const avMemoryDescriptor_t, const avTensorDescriptor_t, avMemoryDescriptor_t)
-		{
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		}
 		avStatus_t cudaMetricFunction(avContextDescriptor_t, avMetricType_t, const avTensorDescriptor_t, const avMemoryDescriptor_t, const avTensorDescriptor_t, const avMemoryDescriptor_t, void *)
 		{
 			return AVOCADO_STATUS_NOT_SUPPORTED;

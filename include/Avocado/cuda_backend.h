@@ -107,6 +107,15 @@ DLL_PUBLIC avStatus_t cudaConvolutionImplicitGemmForward(avContextDescriptor_t c
 		const avMemoryDescriptor_t zMem, const void *beta, const avTensorDescriptor_t yDesc, avMemoryDescriptor_t yMem,
 		avActivationType_t activation);
 
+/* Explicit lowering: src[N,H,W,C] -> rows[N*Ho*Wo, kh*kw*C], so that rows x w[K, kh*kw*C]^T (cudaGemm with op(B) = T)
+ * is the convolution.  Tap (i, j) of output pixel (oh, ow) holds input pixel (oh + i + padding_h, ow + j + padding_w),
+ * or the descriptor's padding value outside the image; AVOCADO_CROSS_CORRELATION_MODE stores the taps in the opposite
+ * order.  Ho = H - 2*padding_h - (kh - 1).  Any dtype (elements are only moved); stride 1, no dilation.
+ * Replaces ref :791-792 (src/im2row.cu:29-66, :85-125), with which it coincides for the "same" padding
+ * (padding = -kernel/2) the reference's kernel was written for. */
+DLL_PUBLIC avStatus_t cudaIm2Row(avContextDescriptor_t context, const avConvolutionDescriptor_t config, const avTensorDescriptor_t filterDesc,
+		const avTensorDescriptor_t srcDesc, const avMemoryDescriptor_t srcMem, const avTensorDescriptor_t rowDesc, avMemoryDescriptor_t rowMem);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Descriptor and context plumbing  (ref :58-262, :743-780, :992-1034; src/descriptors.cu, src/cuda_properties.cpp)
  * ------------------------------------------------------------------------------------------------------------ */
@@ -226,8 +235,6 @@ DLL_PUBLIC avStatus_t cudaPoolingForward(avContextDescriptor_t context, const av
 DLL_PUBLIC avStatus_t cudaPoolingBackward(avContextDescriptor_t context, const avPoolingDescriptor_t config, const void *alpha, const avTensorDescriptor_t xDesc,
 		const avMemoryDescriptor_t xMem, const avTensorDescriptor_t dyDesc, const avMemoryDescriptor_t dyMem, const void *beta,
 		const avTensorDescriptor_t dxDesc, avMemoryDescriptor_t dxMem);
-DLL_PUBLIC avStatus_t cudaIm2Row(avContextDescriptor_t context, const avConvolutionDescriptor_t config, const avTensorDescriptor_t filterDesc,
-		const avTensorDescriptor_t srcDesc, const avMemoryDescriptor_t srcMem, const avTensorDescriptor_t rowDesc, avMemoryDescriptor_t rowMem);
 DLL_PUBLIC avStatus_t cudaMetricFunction(avContextDescriptor_t context, avMetricType_t metricType, const avTensorDescriptor_t outputDesc,
 		const avMemoryDescriptor_t outputMem, const avTensorDescriptor_t targetDesc, const avMemoryDescriptor_t targetMem, void *result);
 DLL_PUBLIC avStatus_t cudaLossFunction(avContextDescriptor_t context, avLossType_t lossType, const avTensorDescriptor_t outputDesc,

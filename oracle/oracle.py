@@ -195,6 +195,33 @@ def winograd_update_transform(matrices, transform_size, kernel_size, dw=None, al
     return out
 
 
+def im2row(x, kernel=(3, 3), padding=(-1, -1), rotate=False, padding_value=0):
+    """rows[N*Ho*Wo, kh*kw*C] of the explicit lowering (reference src/im2row.cu:29-66, restated as a gather).
+
+    Tap (i, j) of an output pixel (oh, ow) reads input pixel (oh + i + padding_h, ow + j + padding_w); pixels outside the
+    image hold padding_value; rotate=True (CROSS_CORRELATION_MODE) stores the taps in the opposite order.  Works on any
+    dtype: values are only moved.  Pure numpy, small cases only.
+    """
+    x = np.asarray(x)
+    N, H, W, C = x.shape
+    kh, kw = kernel
+    Ho, Wo = H - 2 * padding[0] - (kh - 1), W - 2 * padding[1] - (kw - 1)
+    rows = np.empty((N, Ho, Wo, kh * kw, C), dtype=x.dtype)
+    for i in range(kh):
+        for j in range(kw):
+            tap = i * kw + j
+            src = (kh * kw - 1 - tap) if rotate else tap
+            si, sj = divmod(src, kw)
+            plane = np.full((N, Ho, Wo, C), padding_value, dtype=x.dtype)
+            h0, w0 = si + padding[0], sj + padding[1]          # input coordinate of output (0, 0)
+            oh_lo, oh_hi = max(0, -h0), min(Ho, H - h0)
+            ow_lo, ow_hi = max(0, -w0), min(Wo, W - w0)
+            if oh_hi > oh_lo and ow_hi > ow_lo:
+                plane[:, oh_lo:oh_hi, ow_lo:ow_hi, :] = x[:, oh_lo + h0:oh_hi + h0, ow_lo + w0:ow_hi + w0, :]
+            rows[:, :, :, tap, :] = plane
+    return rows.reshape(N * Ho * Wo, kh * kw * C)
+
+
 def gemm_batched(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
     """C[i] = alpha * op(A[i]) * op(B[i]) + beta * C[i] in float64 (row-major 3-D arrays)."""
     a, b = _f64(a), _f64(b)
