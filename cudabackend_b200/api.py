@@ -83,14 +83,17 @@ SIGNATURES = {
     "cudaConvolutionWinogradFusedForwardNoAlloc": (_INT, _conv_args),
     "cudaRunBoundedWaitSelfTest": (_INT, [_H, _INT]),
     "cudaIm2Row": (_INT, [_H, _H, _H, _H, _H, _H, _H]),
+    "cudaOptimizerLearn": (_INT, [_H, _H, _VP, _H, _H, _VP, _H, _H, _H]),
+    "cudaAddBias": (_INT, [_H, _VP, _VP, _H, _H, _H, _H, _H, _H, _VP, _VP, _VP, _H, _INT]),
+    "cudaActivationForward": (_INT, [_H, _INT, _VP, _H, _H, _VP, _H, _H]),
 }
 
 # exported for link compatibility, return NOT_SUPPORTED
 UNSUPPORTED_SYMBOLS = ["cudaChangeType", "cudaConcatTensors", "cudaSplitTensors", "cudaTranspose", "cudaScaleTensor", "cudaAddScalarToTensor",
-                       "cudaAddTensors", "cudaAddBias", "cudaBinaryOp", "cudaUnaryOp", "cudaReduceTensor", "cudaActivationForward",
+                       "cudaAddTensors", "cudaBinaryOp", "cudaUnaryOp", "cudaReduceTensor",
                        "cudaActivationBackward", "cudaSoftmaxForward", "cudaSoftmaxBackward", "cudaAffineForward", "cudaBatchNormInference",
                        "cudaBatchNormForward", "cudaBatchNormBackward", "cudaDropoutForward", "cudaDropoutBackward", "cudaPoolingForward",
-                       "cudaPoolingBackward", "cudaMetricFunction", "cudaLossFunction", "cudaLossGradient", "cudaOptimizerLearn",
+                       "cudaPoolingBackward", "cudaMetricFunction", "cudaLossFunction", "cudaLossGradient",
                        "cudaRegularizerL2"]
 
 

@@ -39,10 +39,6 @@ namespace avocado
 		{
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
-		avStatus_t cudaAddBias(avContextDescriptor_t, const void *, const void *, const avTensorDescriptor_t, const avMemoryDescriptor_t, const avTensorDescriptor_t, const avMemoryDescriptor_t, const avTensorDescriptor_t, avMemoryDescriptor_t, const void *, const void *, const void *, const avMemoryDescriptor_t, avActivationType_t)
-		{
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		}
 		avStatus_t cudaBinaryOp(avContextDescriptor_t, avBinaryOp_t, const void *, const avTensorDescriptor_t, const avMemoryDescriptor_t, const void *, const avTensorDescriptor_t, const avMemoryDescriptor_t, const void *, const avTensorDescriptor_t, avMemoryDescriptor_t)
 		{
 			return AVOCADO_STATUS_NOT_SUPPORTED;
@@ -52,10 +48,6 @@ namespace avocado
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
 		avStatus_t cudaReduceTensor(avContextDescriptor_t, avReduceOp_t, const void *, const avTensorDescriptor_t, const avMemoryDescriptor_t, const void *, const avTensorDescriptor_t, avMemoryDescriptor_t)
-		{
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		}
-		avStatus_t cudaActivationForward(avContextDescriptor_t, avActivationType_t, const void *, const avTensorDescriptor_t, const avMemoryDescriptor_t, const void *, const avTensorDescriptor_t, avMemoryDescriptor_t)
 		{
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
@@ -112,10 +104,6 @@ namespace avocado
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
 		avStatus_t cudaLossGradient(avContextDescriptor_t, avLossType_t, const void *, const avTensorDescriptor_t, const avMemoryDescriptor_t, const avTensorDescriptor_t, const avMemoryDescriptor_t, const void *, const avTensorDescriptor_t, avMemoryDescriptor_t, bool)
-		{
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		}
-		avStatus_t cudaOptimizerLearn(avContextDescriptor_t, const avOptimizerDescriptor_t, const void *, const avTensorDescriptor_t, const avTensorDescriptor_t, const void *, const avTensorDescriptor_t, avMemoryDescriptor_t, avMemoryDescriptor_t)
 		{
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		}

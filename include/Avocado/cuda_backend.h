@@ -116,6 +116,26 @@ DLL_PUBLIC avStatus_t cudaConvolutionImplicitGemmForward(avContextDescriptor_t c
 DLL_PUBLIC avStatus_t cudaIm2Row(avContextDescriptor_t context, const avConvolutionDescriptor_t config, const avTensorDescriptor_t filterDesc,
 		const avTensorDescriptor_t srcDesc, const avMemoryDescriptor_t srcMem, const avTensorDescriptor_t rowDesc, avMemoryDescriptor_t rowMem);
 
+/* y = alpha1 * activation(alpha2 * x + b + beta1 * z) + beta2 * z + beta3 * y, b broadcast over the leading dimensions of
+ * x; b is float32 for float16 / bfloat16 / float32 tensors and float64 for float64 ones; z is optional.  The step that
+ * follows a convolution whose epilogue was not fused.  Replaces ref :380-383 (src/tensor_op.cu:199-228, :493-551). */
+DLL_PUBLIC avStatus_t cudaAddBias(avContextDescriptor_t context, const void *alpha1, const void *alpha2, const avTensorDescriptor_t xDesc,
+		const avMemoryDescriptor_t xMem, const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem, const avTensorDescriptor_t yDesc,
+		avMemoryDescriptor_t yMem, const void *beta1, const void *beta2, const void *beta3, const avMemoryDescriptor_t zMem, avActivationType_t activation);
+
+/* y = alpha * activation(x) + beta * y, in place allowed.  float16, bfloat16, float32, float64.  Replaces ref :490-491. */
+DLL_PUBLIC avStatus_t cudaActivationForward(avContextDescriptor_t context, avActivationType_t activation, const void *alpha, const avTensorDescriptor_t xDesc,
+		const avMemoryDescriptor_t xMem, const void *beta, const avTensorDescriptor_t yDesc, avMemoryDescriptor_t yMem);
+
+/* The weight update after the gradient all-reduce of a training step: w = alpha * step(dw) + beta * w with SGD (optional
+ * momentum / Nesterov; one buffer of w's size in `workspace`) or Adam (two buffers).  float32 / float64.  `dwMem` is a
+ * memory handle (the reference's prototype types it as a tensor handle; both are the same integer type).  Adam's bias
+ * correction uses t = steps + 1 and increments the descriptor's step count.  Replaces ref :1049-1051
+ * (src/optimizers.cu:34-70, :71-160, :168-186). */
+DLL_PUBLIC avStatus_t cudaOptimizerLearn(avContextDescriptor_t context, const avOptimizerDescriptor_t config, const void *alpha,
+		const avTensorDescriptor_t dwDesc, const avTensorDescriptor_t dwMem, const void *beta, const avTensorDescriptor_t wDesc, avMemoryDescriptor_t wMem,
+		avMemoryDescriptor_t workspace);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Descriptor and context plumbing  (ref :58-262, :743-780, :992-1034; src/descriptors.cu, src/cuda_properties.cpp)
  * ------------------------------------------------------------------------------------------------------------ */
@@ -162,7 +182,7 @@ DLL_PUBLIC avStatus_t cudaSetConvolutionDescriptor(avConvolutionDescriptor_t des
 DLL_PUBLIC avStatus_t cudaGetConvolutionDescriptor(avConvolutionDescriptor_t desc, avConvolutionMode_t *mode, int *nbDims, int padding[], int strides[],
 		int dilation[], int *groups, void *paddingValue);
 
-/* Optimizer descriptors (ref :992-1034): stored and returned; the update itself is outside this library's path. */
+/* Optimizer descriptors (ref :992-1034); the update itself is cudaOptimizerLearn above. */
 DLL_PUBLIC avStatus_t cudaCreateOptimizerDescriptor(avOptimizerDescriptor_t *result);
 DLL_PUBLIC avStatus_t cudaDestroyOptimizerDescriptor(avOptimizerDescriptor_t desc);
 DLL_PUBLIC avStatus_t cudaSetOptimizerDescriptor(avOptimizerDescriptor_t desc, avOptimizerType_t type, av_int64 steps, double learningRate,
@@ -189,9 +209,6 @@ DLL_PUBLIC avStatus_t cudaAddScalarToTensor(avContextDescriptor_t context, const
 		const void *scalar, const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem);
 DLL_PUBLIC avStatus_t cudaAddTensors(avContextDescriptor_t context, const void *alpha, const avTensorDescriptor_t aDesc, const avMemoryDescriptor_t aMem,
 		const void *beta, const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem);
-DLL_PUBLIC avStatus_t cudaAddBias(avContextDescriptor_t context, const void *alpha1, const void *alpha2, const avTensorDescriptor_t xDesc,
-		const avMemoryDescriptor_t xMem, const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem, const avTensorDescriptor_t yDesc,
-		avMemoryDescriptor_t yMem, const void *beta1, const void *beta2, const void *beta3, const avMemoryDescriptor_t zMem, avActivationType_t activation);
 DLL_PUBLIC avStatus_t cudaBinaryOp(avContextDescriptor_t context, avBinaryOp_t operation, const void *alpha1, const avTensorDescriptor_t aDesc,
 		const avMemoryDescriptor_t aMem, const void *alpha2, const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem, const void *beta,
 		const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem);
@@ -199,8 +216,6 @@ DLL_PUBLIC avStatus_t cudaUnaryOp(avContextDescriptor_t context, avUnaryOp_t ope
 		const avMemoryDescriptor_t aMem, const void *beta, const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem);
 DLL_PUBLIC avStatus_t cudaReduceTensor(avContextDescriptor_t context, avReduceOp_t operation, const void *alpha, const avTensorDescriptor_t aDesc,
 		const avMemoryDescriptor_t aMem, const void *beta, const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem);
-DLL_PUBLIC avStatus_t cudaActivationForward(avContextDescriptor_t context, avActivationType_t activation, const void *alpha, const avTensorDescriptor_t xDesc,
-		const avMemoryDescriptor_t xMem, const void *beta, const avTensorDescriptor_t yDesc, avMemoryDescriptor_t yMem);
 DLL_PUBLIC avStatus_t cudaActivationBackward(avContextDescriptor_t context, avActivationType_t activation, const void *alpha, const avTensorDescriptor_t yDesc,
 		const avMemoryDescriptor_t yMem, const avTensorDescriptor_t dyDesc, const avMemoryDescriptor_t dyMem, const void *beta,
 		const avTensorDescriptor_t dxDesc, avMemoryDescriptor_t dxMem);
@@ -242,9 +257,6 @@ DLL_PUBLIC avStatus_t cudaLossFunction(avContextDescriptor_t context, avLossType
 DLL_PUBLIC avStatus_t cudaLossGradient(avContextDescriptor_t context, avLossType_t lossType, const void *alpha, const avTensorDescriptor_t outputDesc,
 		const avMemoryDescriptor_t outputMem, const avTensorDescriptor_t targetDesc, const avMemoryDescriptor_t targetMem, const void *beta,
 		const avTensorDescriptor_t gradientDesc, avMemoryDescriptor_t gradientMem, bool isFused);
-DLL_PUBLIC avStatus_t cudaOptimizerLearn(avContextDescriptor_t context, const avOptimizerDescriptor_t config, const void *alpha,
-		const avTensorDescriptor_t dwDesc, const avTensorDescriptor_t dwMem, const void *beta, const avTensorDescriptor_t wDesc, avMemoryDescriptor_t wMem,
-		avMemoryDescriptor_t workspace);
 DLL_PUBLIC avStatus_t cudaRegularizerL2(avContextDescriptor_t context, const avTensorDescriptor_t gradientDesc, avMemoryDescriptor_t dwMem,
 		const avTensorDescriptor_t wDesc, const avMemoryDescriptor_t wMem, const void *scale, const void *offset, void *loss);
 

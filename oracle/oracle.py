@@ -195,6 +195,44 @@ def winograd_update_transform(matrices, transform_size, kernel_size, dw=None, al
     return out
 
 
+def activation(x, name):
+    """The nine activations of the reference (src/activations.cuh:202-425) in float64 numpy; same formulas as the C oracle."""
+    x = np.asarray(x, dtype=np.float64)
+    if name == "linear":
+        return x
+    if name == "sigmoid":
+        return 1.0 / (1.0 + np.exp(-x))
+    if name == "tanh":
+        return np.tanh(x)
+    if name == "relu":
+        return np.maximum(x, 0.0)
+    if name == "selu":
+        return np.where(x >= 0, float(np.float32(1.05070098)) * x, float(np.float32(1.05070098)) * float(np.float32(1.67326324)) * np.expm1(x))
+    if name == "elu":
+        return np.where(x >= 0, x, np.expm1(x))
+    if name == "exponential":
+        return np.exp(x)
+    if name == "softplus":
+        return np.log1p(np.exp(x))
+    if name == "softsign":
+        return x / (np.abs(x) + 1.0)
+    raise ValueError(name)
+
+
+def add_bias(x, bias, z=None, y=None, alpha1=1.0, alpha2=1.0, beta1=0.0, beta2=0.0, beta3=0.0, act="linear"):
+    """y = alpha1 * act(alpha2 * x + b + beta1 * z) + beta2 * z + beta3 * y  (reference src/tensor_op.cu:199-228), float64."""
+    x = np.asarray(x, dtype=np.float64)
+    t = alpha2 * x + np.asarray(bias, dtype=np.float64)
+    if z is not None and (beta1 != 0.0 or beta2 != 0.0):
+        z = np.asarray(z, dtype=np.float64)
+        t = alpha1 * activation(t + beta1 * z, act) + beta2 * z
+    else:
+        t = alpha1 * activation(t, act)
+    if beta3 != 0.0:
+        t = t + beta3 * np.asarray(y, dtype=np.float64)
+    return t
+
+
 def im2row(x, kernel=(3, 3), padding=(-1, -1), rotate=False, padding_value=0):
     """rows[N*Ho*Wo, kh*kw*C] of the explicit lowering (reference src/im2row.cu:29-66, restated as a gather).
 
@@ -220,6 +258,37 @@ def im2row(x, kernel=(3, 3), padding=(-1, -1), rotate=False, padding_value=0):
                 plane[:, oh_lo:oh_hi, ow_lo:ow_hi, :] = x[:, oh_lo + h0:oh_hi + h0, ow_lo + w0:ow_hi + w0, :]
             rows[:, :, :, tap, :] = plane
     return rows.reshape(N * Ho * Wo, kh * kw * C)
+
+
+def optimizer_learn(kind, w, dw, state, learning_rate, coef=(0.0, 0.0), momentum=False, nesterov=False, steps=0, alpha=1.0, beta=0.0, eps=None):
+    """One weight update in float64 (reference src/optimizers.cu:34-70 and :111-160); returns (w, state).
+
+    kind "sgd": state = momentum buffer or None; kind "adam": state = (m, v), bias correction at t = steps + 1.
+    eps: the flush-to-zero threshold and Adam's epsilon (machine epsilon of the tensor dtype on the device).
+    """
+    w = np.asarray(w, dtype=np.float64)
+    dw = np.asarray(dw, dtype=np.float64)
+    eps = np.finfo(np.float32).eps if eps is None else eps
+    if kind == "sgd":
+        if momentum:
+            m = coef[0] * state - learning_rate * dw
+            step = coef[0] * m - learning_rate * dw if nesterov else m
+            state = m
+        else:
+            step = -learning_rate * dw
+    else:
+        m, v = state
+        m = m * coef[0] + dw * (1.0 - coef[0])
+        v = v * coef[1] + dw * dw * (1.0 - coef[1])
+        t = steps + 1
+        lr = learning_rate
+        if t < 10000:
+            lr = lr * np.sqrt(1.0 - coef[1] ** t) / (1.0 - coef[0] ** t)
+        step = -m * lr / np.sqrt(v + eps)
+        state = (m, v)
+    out = alpha * step + beta * w
+    out = np.where(np.abs(out) < eps, 0.0, out)
+    return out, state
 
 
 def gemm_batched(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
