@@ -28,7 +28,6 @@
 #include "winograd_tables.cuh"
 
 #include <algorithm>
-#include <type_traits>
 
 namespace
 {
@@ -102,7 +101,6 @@ namespace
 	{
 		return static_cast<float>(winograd::Coefficients<2, 3>::output(row, col));
 	}
-	template<int COL>
 	__device__ __forceinline__ float column_transform(int a, float m0, float m1, float m2, float m3)
 	{
 		/* sum over xi of A^T[a][xi] * M[xi][nu] */
@@ -160,8 +158,8 @@ namespace
 #pragma unroll
 			for (int j = 0; j < 8; j++)
 			{
-				const float t0 = column_transform<NU>(0, m0[j], m1[j], m2[j], m3[j]);
-				const float t1 = column_transform<NU>(1, m0[j], m1[j], m2[j], m3[j]);
+				const float t0 = column_transform(0, m0[j], m1[j], m2[j], m3[j]);
+				const float t1 = column_transform(1, m0[j], m1[j], m2[j], m3[j]);
 				accumulate_group<NU>(out, s * 8 + j, t0, t1);
 			}
 		}
