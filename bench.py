@@ -160,13 +160,13 @@ def cpu_sample(cfg, images):
     return seconds, passes * 2.0 * images * cfg["h"] * cfg["w"] * cfg["k"] * cfg["c"] * 9
 
 
-def cpu_baseline(cfg, budget_images):
+def cpu_baseline(cfg, sample_images):
     from oracle import oracle as o
-    seconds, flops = cpu_sample(cfg, budget_images)
+    seconds, flops = cpu_sample(cfg, sample_images)
     return {"value": flops / seconds / 1e12, "unit": "TFLOP/s (effective, direct-conv FLOP count)", "cores": o.max_threads(), "kind": "port",
-            "sample": "%d of %d images of the workload, naive direct convolution (OpenMP over image x output row), %.2f s" % (budget_images, cfg["n"],
+            "sample": "%d of %d images of the workload, naive direct convolution (OpenMP over image x output row), %.2f s" % (sample_images, cfg["n"],
                                                                                                                           seconds),
-            "images_per_s": budget_images / seconds}
+            "images_per_s": sample_images / seconds}
 
 
 def run_reference_arm(args, cfg, rank):
@@ -200,15 +200,18 @@ class Workload:
     """One buffer set (context + tensors) of the configured convolution; several are rotated so that a step never
     finds its inputs in L2 from the step before."""
 
-    def __init__(self, cfg, device, matrices_dtype, data):
+    def __init__(self, cfg, device, matrices_dtype, data, side_stream=False):
         from cudabackend_b200 import api, pipeline
         self.api = api
         self.cfg = cfg
         self.ctx = api.Context(device)
+        # a second context for the weight transform, which depends on nothing the input transform touches
+        self.side_ctx = api.Context(device) if (side_stream and cfg["kind"] == "winograd_nonfused") else None
         n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
         kind = cfg["kind"]
         if kind in ("winograd_nonfused", "training"):
-            self.p = pipeline.WinogradNonFused(self.ctx, n, h, w, c, k, cfg["dtype"], matrices_dtype, 4, 3, device=device, training=(kind == "training"))
+            self.p = pipeline.WinogradNonFused(self.ctx, n, h, w, c, k, cfg["dtype"], matrices_dtype, 4, 3, device=device, training=(kind == "training"),
+                                               side_ctx=self.side_ctx)
             self.p.x.upload(self.ctx, data["x"])
             self.p.wt.upload(self.ctx, data["w"])
             if kind == "training":
@@ -246,6 +249,9 @@ class Workload:
         return [("implicit_gemm", p.implicit_gemm)]
 
     def step(self):
+        if self.cfg["kind"] == "winograd_nonfused":
+            self.p.forward()  # the four calls of stages(); the weight transform goes to the side context when there is one
+            return
         for _, fn in self.stages():
             fn()
 
@@ -294,7 +300,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     data = synthetic(cfg, seed_offset=rank)
 
     rotation = args.rotation
-    sets = [Workload(cfg, local_rank, matrices_dtype if cfg["kind"] in ("winograd_nonfused", "training") else None, data) for _ in range(rotation)]
+    sets = [Workload(cfg, local_rank, matrices_dtype if cfg["kind"] in ("winograd_nonfused", "training") else None, data, side_stream=args.side_stream)
+            for _ in range(rotation)]
     streams = [torch.cuda.ExternalStream(ws.ctx.stream(), device=local_rank) for ws in sets]
 
     grad_views = None
@@ -481,7 +488,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             "host_wall_ms_per_step": wall_ms / args.steps,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "images_per_s": cfg["n"] * args.steps * world / e2e_s, "ms_per_step": 1e3 * e2e_s / args.steps},
-            "gpu_launches": sets[0].launches_per_step() * args.steps, "launch_mode": "cuda graph, one launch per step" if use_graph else "kernel by kernel",
+            "gpu_launches": sets[0].launches_per_step() * args.steps, "launch_mode": ("cuda graph, one launch per step" if use_graph else "kernel by kernel")
+            + ("; weight transform on a second context (parallel graph branch)" if sets[0].side_ctx is not None else ""),
             "stage_ms": stage_ms, "clocks": clocks}
 
     # roofline of the dominant kernel
@@ -556,6 +564,8 @@ def main():
     parser.add_argument("--rotation", type=int, default=4, help="buffer sets rotated between steps")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     parser.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a captured graph")
+    parser.add_argument("--side-stream", action="store_true",
+                        help="issue the weight transform on a second context (a parallel branch of the captured graph); measured slower, off by default")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -82,6 +82,7 @@ SIGNATURES = {
     "cudaDestroyCapturedGraph": (_INT, [_I64]),
     "cudaConvolutionWinogradFusedForwardNoAlloc": (_INT, _conv_args),
     "cudaRunBoundedWaitSelfTest": (_INT, [_H, _INT]),
+    "cudaContextWaitForContext": (_INT, [_H, _H]),
     "cudaIm2Row": (_INT, [_H, _H, _H, _H, _H, _H, _H]),
     "cudaOptimizerLearn": (_INT, [_H, _H, _VP, _H, _H, _VP, _H, _H, _H]),
     "cudaAddBias": (_INT, [_H, _VP, _VP, _H, _H, _H, _H, _H, _H, _VP, _VP, _VP, _H, _INT]),
@@ -180,6 +181,10 @@ class Context:
         r = _INT(0)
         call("cudaGetLastDeviceStatus", self.handle, ctypes.byref(r))
         return int(r.value)
+
+    def wait_for(self, other):
+        """Work enqueued on this context from now on runs after the work already enqueued on `other` (no host blocking)."""
+        call("cudaContextWaitForContext", self.handle, other.handle)
 
     def capture(self, fn):
         """Runs fn() once for its side effects on the stream, then records a second run of it into a graph."""

@@ -135,6 +135,8 @@ namespace avocado
 					cudaFree(workspace);
 				if (device_status != nullptr)
 					cudaFree(device_status);
+				if (order_event != nullptr)
+					cudaEventDestroy(order_event);
 				cudaSetDevice(previous);
 			}
 			void ContextObject::setDevice() const
@@ -152,7 +154,6 @@ namespace avocado
 						cudaFree(workspace);
 					workspace = nullptr;
 					workspace_size = 0;
-					cached_weights = nullptr;
 					const size_t rounded = (bytes + 0xFFFFFu) & ~static_cast<size_t>(0xFFFFFu);
 					if (cudaMalloc(&workspace, rounded) != cudaSuccess)
 					{
@@ -842,6 +843,25 @@ namespace avocado
 					return AVOCADO_STATUS_EXECUTION_FAILED;
 				cudaMemset(ctx.device_status, 0, sizeof(int));
 				result[0] = value;
+				return AVOCADO_STATUS_SUCCESS;
+			AVOCADO_API_END
+		}
+
+		avStatus_t cudaContextWaitForContext(avContextDescriptor_t waiting, avContextDescriptor_t signalling)
+		{
+			AVOCADO_API_BEGIN
+				ContextObject &later = getContext(waiting);
+				ContextObject &earlier = getContext(signalling);
+				if (&later == &earlier)
+					return AVOCADO_STATUS_SUCCESS; /* a stream is ordered with itself */
+				earlier.setDevice();
+				if (earlier.order_event == nullptr and cudaEventCreateWithFlags(&earlier.order_event, cudaEventDisableTiming) != cudaSuccess)
+					return checkForErrors();
+				if (cudaEventRecord(earlier.order_event, earlier.getStream()) != cudaSuccess)
+					return checkForErrors();
+				later.setDevice();
+				if (cudaStreamWaitEvent(later.getStream(), earlier.order_event, 0) != cudaSuccess)
+					return checkForErrors();
 				return AVOCADO_STATUS_SUCCESS;
 			AVOCADO_API_END
 		}

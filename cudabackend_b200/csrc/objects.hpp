@@ -161,9 +161,7 @@ namespace avocado
 				void *workspace = nullptr;
 				size_t workspace_size = 0;
 				int *device_status = nullptr;
-				/* identity of the weights whose transformed copy currently sits at the start of the workspace */
-				const void *cached_weights = nullptr;
-				uint64_t cached_weights_tag = 0;
+				cudaEvent_t order_event = nullptr; /* recorded on this stream when another context waits for this one */
 
 				explicit ContextObject(int deviceIndex, bool isDefault);
 				~ContextObject();

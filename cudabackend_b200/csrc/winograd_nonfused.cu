@@ -483,8 +483,8 @@ namespace
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 
 		auto kernel = f43::kernel_input_tma<TS, T, MT>;
-		constexpr int ring_budget = 96 * 1024; /* shared memory per block for the halo ring: two blocks per SM stay resident */
-		g.stages = std::max(2, std::min(f43::kMaxStages, ring_budget / g.stage_bytes));
+		constexpr int ring_bytes = 96 * 1024; /* shared memory per block for the halo ring: two blocks per SM stay resident */
+		g.stages = std::max(2, std::min(f43::kMaxStages, ring_bytes / g.stage_bytes));
 		const int smem_bytes = g.stages * g.stage_bytes + 128;
 		static bool configured[kMaxDevices] = { };
 		if (not configured[ctx.device])

@@ -29,8 +29,12 @@ class WinogradNonFused:
     `dtype`, or "float32" with 16-bit tensors).
     """
 
-    def __init__(self, ctx, n, h, w, c, k, dtype, matrices_dtype=None, transform_size=4, kernel_size=3, padding=None, device=0, training=False):
+    def __init__(self, ctx, n, h, w, c, k, dtype, matrices_dtype=None, transform_size=4, kernel_size=3, padding=None, device=0, training=False,
+                 side_ctx=None):
         self.ctx = ctx
+        # optional second context: the weight transform depends on nothing the input transform touches, so forward() issues
+        # it there and joins before the contraction (a parallel branch when the step is captured into a graph)
+        self.side_ctx = side_ctx
         self.n, self.h, self.w, self.c, self.k = n, h, w, c, k
         self.ts, self.ks = transform_size, kernel_size
         self.dtype = dtype
@@ -67,9 +71,9 @@ class WinogradNonFused:
         return self.z.upload(self.ctx, values)
 
     # ---- individual stages --------------------------------------------------------------------------------
-    def weight_transform(self, rotated=False):
+    def weight_transform(self, rotated=False, ctx=None):
         conv = self.conv_rotated if rotated else self.conv
-        api.call("cudaWinogradWeightTransform", self.ctx.handle, conv.handle, self.ts, self.wt.desc.handle, self.wt.mem.handle, self.u.desc.handle,
+        api.call("cudaWinogradWeightTransform", (ctx or self.ctx).handle, conv.handle, self.ts, self.wt.desc.handle, self.wt.mem.handle, self.u.desc.handle,
                  self.u.mem.handle)
 
     def input_transform(self, source=None, dest=None):
@@ -109,9 +113,15 @@ class WinogradNonFused:
 
     # ---- whole passes ------------------------------------------------------------------------------------
     def forward(self, activation="linear", transform_weights=True):
-        if transform_weights:
+        side = self.side_ctx if transform_weights else None
+        if side is not None:
+            side.wait_for(self.ctx)                  # U may still be read by this context's previous contraction
+            self.weight_transform(ctx=side)
+        elif transform_weights:
             self.weight_transform()
         self.input_transform()
+        if side is not None:
+            self.ctx.wait_for(side)
         self.gemm(self.v, self.u, self.m, False, True)
         self.output_transform(activation=activation)
 

@@ -46,6 +46,14 @@ DLL_PUBLIC avStatus_t cudaGetLastDeviceStatus(avContextDescriptor_t context, int
  * No counterpart in the reference. */
 DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, int limitMicroseconds);
 
+/* Orders two contexts on the device without blocking the host: everything enqueued on `waiting` after this call runs
+ * after everything enqueued on `signalling` before it.  The reference has only cudaSynchronizeWithContext, which blocks
+ * the calling thread; with this a caller can run independent steps on two contexts (for instance the weight transform
+ * next to the input transform of the same layer) and join them.  Inside a capture (below) the second context's work
+ * becomes a parallel branch of the captured graph: let it wait for the capturing context first, and let the capturing
+ * context wait for it before the capture ends.  No counterpart in the reference. */
+DLL_PUBLIC avStatus_t cudaContextWaitForContext(avContextDescriptor_t waiting, avContextDescriptor_t signalling);
+
 /* Records the work that API calls enqueue on a context instead of running it, and replays it later with one launch.
  * Between Begin and End every call on `context` is captured into a CUDA graph; host scalars (alpha, beta) are read at
  * capture time and baked in; the memory handles used must stay alive while the graph exists.  Run the same call

@@ -72,3 +72,33 @@ def test_context_ready_and_properties(ctx):
     api.call("cudaGetDeviceProperty", 0, 1, ctypes.cast(sms, ctypes.c_void_p))
     assert sms[0] > 0
     assert ctx.last_device_status() == 0
+
+
+def test_contexts_can_be_ordered_without_blocking_the_host(library, device_count):
+    """cudaContextWaitForContext: work on one context runs after work on another; also as parallel branches of a captured graph"""
+    if device_count == 0:
+        pytest.skip("no CUDA device visible")
+    import numpy as np
+    from cudabackend_b200 import pipeline
+    from oracle import oracle as o
+    from tests import common
+    main, side = api.Context(0), api.Context(0)
+    p = pipeline.WinogradNonFused(main, 4, 16, 16, 64, 64, "float16", "float32", 4, 3, side_ctx=side)
+    x = p.x.upload(main, common.uniform("x", p.x.shape))
+    w1 = common.he_normal_weights(64, 3, 64)
+    wt = p.wt.upload(main, w1)
+    main.synchronize()
+    p.forward()                                     # weight transform on `side`, joined before the contraction
+    ref = o.conv2d_forward(x, wt)
+    assert o.error_metrics(p.y.download(main), ref)["elem"] <= 1e-2
+    graph = main.capture(p.forward)                 # the same with the side branch captured into the graph
+    for scale in (2.0, -0.5):
+        wt = p.wt.upload(main, w1 * scale)
+        p.y.mem.zero(main)
+        main.synchronize()
+        graph.launch()
+        main.synchronize()
+        assert o.error_metrics(p.y.download(main), o.conv2d_forward(x, wt))["elem"] <= 1e-2
+    graph.destroy()
+    side.destroy()
+    main.destroy()
