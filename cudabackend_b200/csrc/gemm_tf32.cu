@@ -9,7 +9,8 @@
  *
  * Roles of the 10 warps of a CTA (persistent over output tiles of 128 rows x BLOCK_N columns):
  *   warp 0      TMA producer: raw float32 tiles of A (128 x 32) and B (BLOCK_N x 32) into a ring of stages
- *   warps 2-5   splitters: rewrite each landed tile in place as hi and write lo beside it, fence for the async proxy
+ *   warps 2-5   splitters: rewrite each landed tile in place as hi and write lo beside it, fence for the async proxy;
+ *               every warp waits for the stage by itself and owns a fixed quarter of it (no barrier between them)
  *   warp 1      issues the MMAs for a stage once it is split, releases the stage when they complete
  *   warps 6-9   epilogue: tcgen05.ld -> alpha -> 128-byte-swizzled shared memory -> TMA store
  *
