@@ -553,7 +553,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                             "hbm_gbs": algorithmic / step_s / 1e9}
 
     if world == 1 and not args.no_cpu:
-        images = {2: 32, 3: 32, 4: 32, 5: 8}[args.config]
+        images = {2: 64, 3: 64, 4: 64, 5: 16}[args.config]
         line["cpu_baseline"] = cpu_baseline(cfg, images)
     print(json.dumps(line))
     if world > 1:
