@@ -165,7 +165,9 @@ namespace
 		}
 	}
 
-	template<typename T>
+	/* SIMPLE: no z, beta == 0, linear or relu activation -- the epilogue of the common inference layer, without the
+	 * per-vector decisions of the general form */
+	template<typename T, bool SIMPLE>
 	__global__ void __launch_bounds__(kThreads, 1) kernel_f23_contract_output(const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapU,
 			F23Params p, int *deviceStatus)
 	{
@@ -405,6 +407,16 @@ namespace
 							r[5] = fmaf(p.alpha1, out[a][b][8 * v + 5], b1.y);
 							r[6] = fmaf(p.alpha1, out[a][b][8 * v + 6], b1.z);
 							r[7] = fmaf(p.alpha1, out[a][b][8 * v + 7], b1.w);
+							if constexpr (SIMPLE)
+							{
+								const bool relu = activation == AVOCADO_ACTIVATION_RELU;
+#pragma unroll
+								for (int q = 0; q < 8; q++)
+									r[q] = relu ? fmaxf(r[q], 0.0f) : r[q]; /* a select, not a branch */
+								*reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(pack2(r[0], r[1], T()), pack2(r[2], r[3], T()), pack2(r[4], r[5], T()),
+										pack2(r[6], r[7], T()));
+								continue;
+							}
 							if (z != nullptr)
 							{
 								const uint4 raw = *reinterpret_cast<const uint4*>(z + index + 8 * v);
@@ -461,11 +473,13 @@ namespace
 	template<typename T>
 	avStatus_t launch_typed(ContextObject &ctx, const CUtensorMap &mapV, const CUtensorMap &mapU, const F23Params &p, int *deviceStatus)
 	{
-		auto kernel = kernel_f23_contract_output<T>;
+		const bool simple = p.z == nullptr and p.beta == 0.0f and (p.activation == AVOCADO_ACTIVATION_LINEAR or p.activation == AVOCADO_ACTIVATION_RELU);
+		auto kernel = simple ? kernel_f23_contract_output<T, true> : kernel_f23_contract_output<T, false>;
 		static bool configured[kMaxDevices] = { };
 		if (not configured[ctx.device])
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+			if (cudaFuncSetAttribute(kernel_f23_contract_output<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess
+					or cudaFuncSetAttribute(kernel_f23_contract_output<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
 				return checkForErrors();
 			configured[ctx.device] = true;
 		}
