@@ -33,7 +33,7 @@ namespace
 
 	struct Im2RowShape
 	{
-			int batch, height, width, row_bytes_per_pixel; /* input; a pixel is channels * element size bytes */
+			int batch, height, width; /* input */
 			int out_height, out_width;
 			int kernel_h, kernel_w;
 			int pad_h, pad_w; /* offsets added to the output coordinate (negative = padding) */
@@ -144,7 +144,6 @@ namespace avocado
 				const long long pixel_bytes = channels * element_size;
 				if (pixel_bytes > 0x7FFFFFFFll)
 					return AVOCADO_STATUS_NOT_SUPPORTED;
-				s.row_bytes_per_pixel = static_cast<int>(pixel_bytes);
 				ctx.setDevice();
 
 				const bool aligned = (pixel_bytes % 16 == 0) and (reinterpret_cast<uintptr_t>(src_ptr) % 16 == 0) and (reinterpret_cast<uintptr_t>(row_ptr) % 16 == 0);
