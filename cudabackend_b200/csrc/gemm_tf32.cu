@@ -7,12 +7,12 @@
  * accumulated as  A_hi*B_hi + A_hi*B_lo + A_lo*B_hi  in a float32 TMEM accumulator: three tcgen05.mma kind::tf32 per
  * 8-deep slice, error about 1e-6 relative.  At the Winograd sizes the kernel stays bound by HBM.
  *
- * Roles of the 10 warps of a CTA (persistent over output tiles of 128 rows x BLOCK_N columns):
+ * Roles of the 14 warps of a CTA (persistent over output tiles of 128 rows x BLOCK_N columns):
  *   warp 0      TMA producer: raw float32 tiles of A (128 x 32) and B (BLOCK_N x 32) into a ring of stages
- *   warps 2-5   splitters: rewrite each landed tile in place as hi and write lo beside it, fence for the async proxy;
- *               every warp waits for the stage by itself and owns a fixed quarter of it (no barrier between them)
+ *   warps 2-9   splitters: rewrite each landed tile in place as hi and write lo beside it, fence for the async proxy;
+ *               every warp waits for the stage by itself and owns a fixed share of it (no barrier between them)
  *   warp 1      issues the MMAs for a stage once it is split, releases the stage when they complete
- *   warps 6-9   epilogue: tcgen05.ld -> alpha -> 128-byte-swizzled shared memory -> TMA store
+ *   warps 10-13 epilogue: tcgen05.ld -> alpha -> 128-byte-swizzled shared memory -> TMA store
  *
  * op(B) = B (the dX contraction of the Winograd backward pass, where B is the small transformed filter tensor) is
  * served by transposing B into the context's scratch buffer first.
@@ -30,7 +30,12 @@ namespace
 
 	constexpr int kBlockM = 128;
 	constexpr int kBlockK = 32; /* float32 elements: 128 bytes */
-	constexpr int kThreads = 320;
+	/* warp 0 producer, warp 1 MMA issuer, then the split warps, then four epilogue warps.  Eight split warps: with four,
+	 * rewriting a stage (24-32 KB, about 20 instructions per 16 bytes) took one warp per scheduler longer than the three
+	 * MMAs per slice that consume it, and the split was the pace-setter of both kernels. */
+	constexpr int kSplitWarps = 8;
+	constexpr int kSplitThreads = kSplitWarps * 32;
+	constexpr int kThreads = 64 + kSplitThreads + 128;
 
 	template<int BLOCK_N, int STAGES>
 	struct Config
@@ -96,7 +101,7 @@ namespace
 			for (int s = 0; s < STAGES; s++)
 			{
 				umma::mbar_init(&full_bar[s], 1);
-				umma::mbar_init(&split_bar[s], 128);
+				umma::mbar_init(&split_bar[s], kSplitThreads);
 				umma::mbar_init(&empty_bar[s], 1);
 			}
 			for (int a = 0; a < 2; a++)
@@ -224,9 +229,9 @@ namespace
 				}
 			}
 		}
-		else if (warp < 6)
+		else if (warp < 2 + kSplitWarps)
 		{
-			/* splitters: 128 threads, each owns every 128th 16-byte chunk of the stage's A and B tiles */
+			/* splitters: each thread owns every kSplitThreads-th 16-byte chunk of the stage's A and B tiles */
 			const int split_thread = threadIdx.x - 64;
 			int stage = 0;
 			uint32_t phase = 0;
@@ -256,7 +261,7 @@ namespace
 					uint4 *b_hi = a_hi + 2 * Cfg::kATile / 16;
 					uint4 *b_lo = b_hi + Cfg::kBTile / 16;
 #pragma unroll 4
-					for (int i = split_thread; i < Cfg::kATile / 16; i += 128)
+					for (int i = split_thread; i < Cfg::kATile / 16; i += kSplitThreads)
 					{
 						uint4 hi, lo;
 						split4(a_hi[i], hi, lo);
@@ -264,7 +269,7 @@ namespace
 						a_lo[i] = lo;
 					}
 #pragma unroll 4
-					for (int i = split_thread; i < Cfg::kBTile / 16; i += 128)
+					for (int i = split_thread; i < Cfg::kBTile / 16; i += kSplitThreads)
 					{
 						uint4 hi, lo;
 						split4(b_hi[i], hi, lo);
@@ -285,7 +290,7 @@ namespace
 		{
 			const int quarter = warp % 4;
 			const int row = quarter * 32 + lane;
-			const int epi_thread = threadIdx.x - 192;
+			const int epi_thread = threadIdx.x - (64 + kSplitThreads);
 			int it = 0;
 			for (int tile = blockIdx.x; tile < numTiles; tile += gridDim.x, it++)
 			{
@@ -449,7 +454,7 @@ namespace
 			for (int s = 0; s < kTnStages; s++)
 			{
 				umma::mbar_init(&full_bar[s], 1);
-				umma::mbar_init(&split_bar[s], 128);
+				umma::mbar_init(&split_bar[s], kSplitThreads);
 				umma::mbar_init(&empty_bar[s], 1);
 			}
 			umma::mbar_init(&tmem_full_bar, 1);
@@ -549,7 +554,7 @@ namespace
 					umma::mma_commit(&tmem_full_bar);
 			}
 		}
-		else if (warp < 6)
+		else if (warp < 2 + kSplitWarps)
 		{
 			const int split_thread = threadIdx.x - 64;
 			int stage = 0;
@@ -575,14 +580,14 @@ namespace
 				uint4 *a_lo = a_hi + a_lo_offset / 16;
 				uint4 *b_hi = a_hi + b_hi_offset / 16;
 				uint4 *b_lo = a_hi + b_lo_offset / 16;
-				for (int i = split_thread; i < a_chunks; i += 128)
+				for (int i = split_thread; i < a_chunks; i += kSplitThreads)
 				{
 					uint4 hi, lo;
 					split4(a_hi[i], hi, lo);
 					a_hi[i] = hi;
 					a_lo[i] = lo;
 				}
-				for (int i = split_thread; i < b_chunks; i += 128)
+				for (int i = split_thread; i < b_chunks; i += kSplitThreads)
 				{
 					uint4 hi, lo;
 					split4(b_hi[i], hi, lo);
