@@ -3,13 +3,15 @@
  *
  * The reference runs float32 transform-domain products through cublasSgemmStridedBatched (src/gemm.cpp:178-185).  A
  * single TF32 pass is not accurate enough for Winograd F(4x4,3x3) (the 10-bit mantissa of the operands costs about
- * 4e-2), so every operand is split in shared memory into a TF32 "hi" part and a TF32 "lo" remainder and the product is
- * accumulated as  A_hi*B_hi + A_hi*B_lo + A_lo*B_hi  in a float32 TMEM accumulator: three tcgen05.mma kind::tf32 per
- * 8-deep slice, error about 1e-6 relative.  At the Winograd sizes the kernel stays bound by HBM.
+ * 4e-2), so every operand is used as a TF32 "hi" part (the landed float32 itself: the MMA ignores the 13 low mantissa
+ * bits) plus a TF32 "lo" remainder written beside it, and the product is accumulated as
+ * A_hi*B_hi + A_hi*B_lo + A_lo*B_hi  in float32 TMEM accumulators: per 8-deep slice one MMA of double width
+ * (A_hi x [B_hi; B_lo]) and one of single width (A_lo x B_hi), error about 1e-6 relative.  The kernels are bound by
+ * shared-memory bandwidth first (copy in, remainder out, operand reads), then by HBM.
  *
  * Roles of the 14 warps of a CTA (persistent over output tiles of 128 rows x BLOCK_N columns):
  *   warp 0      TMA producer: raw float32 tiles of A (128 x 32) and B (BLOCK_N x 32) into a ring of stages
- *   warps 2-9   splitters: rewrite each landed tile in place as hi and write lo beside it, fence for the async proxy;
+ *   warps 2-9   splitters: leave each landed tile as the hi part and write its lo remainder beside it, fence for the async proxy;
  *               every warp waits for the stage by itself and owns a fixed share of it (no barrier between them)
  *   warp 1      issues the MMAs for a stage once it is split, releases the stage when they complete
  *   warps 10-13 epilogue: tcgen05.ld -> alpha -> 128-byte-swizzled shared memory -> TMA store
@@ -48,7 +50,7 @@ namespace
 			static constexpr int kSubTiles = BLOCK_N / 32;
 			static constexpr int kCBytes = kSubTiles * kBlockM * 128;
 			static constexpr int kSmemBytes = STAGES * kStageBytes + kCBytes + 1024;
-			static constexpr int kTmemColumns = 2 * BLOCK_N;
+			static constexpr int kTmemColumns = 4 * BLOCK_N; /* two accumulators of 2 * BLOCK_N columns */
 	};
 
 	/* x rounded to TF32 (10 explicit mantissa bits), ties away from zero like cvt.rna.tf32.f32, with two integer
@@ -58,20 +60,21 @@ namespace
 	{
 		return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u;
 	}
-	/* hi = x rounded to TF32, lo = (x - hi) rounded to TF32; x - hi is exact in float32 */
-	__device__ __forceinline__ void split4(uint4 raw, uint4 &hi, uint4 &lo)
+	/* The "lo" part when the landed float32 itself serves as "hi": kind::tf32 reads the sign, the exponent and the top 10
+	 * mantissa bits of a 32-bit operand and ignores the 13 bits below, so the raw value acts as x truncated to TF32 and
+	 * needs no rewriting; what the MMA then misses is x - trunc(x), exact in float32, rounded to TF32 here.  Half of the
+	 * split's shared-memory writes disappear with it. */
+	__device__ __forceinline__ uint4 remainder4(uint4 raw)
 	{
 		const uint32_t in[4] = { raw.x, raw.y, raw.z, raw.w };
-		uint32_t h[4], l[4];
+		uint32_t l[4];
 #pragma unroll
 		for (int i = 0; i < 4; i++)
 		{
 			const float x = __uint_as_float(in[i]);
-			h[i] = to_tf32(x);
-			l[i] = to_tf32(x - __uint_as_float(h[i]));
+			l[i] = to_tf32(x - __uint_as_float(in[i] & 0xFFFFE000u));
 		}
-		hi = make_uint4(h[0], h[1], h[2], h[3]);
-		lo = make_uint4(l[0], l[1], l[2], l[3]);
+		return make_uint4(l[0], l[1], l[2], l[3]);
 	}
 
 	template<int BLOCK_N, int STAGES>
@@ -179,6 +182,7 @@ namespace
 			if (lane == 0)
 			{
 				constexpr uint32_t idesc = umma::make_instr_desc(umma::kAccumF32, umma::kFormatTF32, umma::kFormatTF32, false, false, kBlockM, BLOCK_N);
+				constexpr uint32_t idesc_wide = umma::make_instr_desc(umma::kAccumF32, umma::kFormatTF32, umma::kFormatTF32, false, false, kBlockM, 2 * BLOCK_N);
 				int stage = 0;
 				uint32_t phase = 0;
 				int it = 0;
@@ -193,7 +197,8 @@ namespace
 						break;
 					}
 					umma::tcgen05_fence_after();
-					const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+					/* 2 * BLOCK_N columns per accumulator: [0, BLOCK_N) collects hi*hi + lo*hi, [BLOCK_N, 2*BLOCK_N) hi*lo */
+					const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * 2 * BLOCK_N);
 					for (int kb = 0; kb < kBlocks; kb++)
 					{
 						if (not umma::mbar_wait(&split_bar[stage], phase, abort_ptr))
@@ -206,16 +211,19 @@ namespace
 						const uint32_t base = umma::smem_u32(smem + stage * Cfg::kStageBytes);
 						const uint64_t a_hi = umma::make_smem_desc(base, 16, 1024, umma::kSwizzle128B);
 						const uint64_t a_lo = umma::make_smem_desc(base + Cfg::kATile, 16, 1024, umma::kSwizzle128B);
+						/* B_hi and B_lo lie one after the other, so one descriptor with N = 2 * BLOCK_N reads both */
 						const uint64_t b_hi = umma::make_smem_desc(base + 2 * Cfg::kATile, 16, 1024, umma::kSwizzle128B);
-						const uint64_t b_lo = umma::make_smem_desc(base + 2 * Cfg::kATile + Cfg::kBTile, 16, 1024, umma::kSwizzle128B);
 #pragma unroll
 						for (int k = 0; k < kBlockK / 8; k++)
 						{
-							/* one MMA consumes 8 float32 = 32 bytes of every row: +2 in descriptor units; small terms first */
+							/* one MMA consumes 8 float32 = 32 bytes of every row: +2 in descriptor units.
+							 * A_hi x [B_hi; B_lo] fills both halves of the accumulator with ONE read of A_hi (an MMA of twice the
+							 * width costs the pipe no more at these widths), A_lo x B_hi adds to the first half: two MMAs and
+							 * 14 KB of operand reads per slice where three separate products need 18 KB.  Shared-memory
+							 * bandwidth, not the tensor pipe, is what this kernel runs out of. */
 							const uint64_t step = static_cast<uint64_t>(2 * k);
-							umma::mma_tf32(tmem_d, a_lo + step, b_hi + step, idesc, (kb | k) != 0);
-							umma::mma_tf32(tmem_d, a_hi + step, b_lo + step, idesc, true);
-							umma::mma_tf32(tmem_d, a_hi + step, b_hi + step, idesc, true);
+							umma::mma_tf32(tmem_d, a_hi + step, b_hi + step, idesc_wide, (kb | k) != 0);
+							umma::mma_tf32(tmem_d, a_lo + step, b_hi + step, idesc, true);
 						}
 						umma::mma_commit(&empty_bar[stage]);
 						if (++stage == STAGES)
@@ -262,20 +270,10 @@ namespace
 					uint4 *b_lo = b_hi + Cfg::kBTile / 16;
 #pragma unroll 4
 					for (int i = split_thread; i < Cfg::kATile / 16; i += kSplitThreads)
-					{
-						uint4 hi, lo;
-						split4(a_hi[i], hi, lo);
-						a_hi[i] = hi;
-						a_lo[i] = lo;
-					}
+						a_lo[i] = remainder4(a_hi[i]);
 #pragma unroll 4
 					for (int i = split_thread; i < Cfg::kBTile / 16; i += kSplitThreads)
-					{
-						uint4 hi, lo;
-						split4(b_hi[i], hi, lo);
-						b_hi[i] = hi;
-						b_lo[i] = lo;
-					}
+						b_lo[i] = remainder4(b_hi[i]);
 					umma::fence_proxy_async_smem();
 					umma::mbar_arrive(&split_bar[stage]);
 					if (++stage == STAGES)
@@ -312,13 +310,17 @@ namespace
 				if (epilogue_go == 0)
 					break;
 				umma::tcgen05_fence_after();
-				const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
+				const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * 2 * BLOCK_N);
 #pragma unroll
 				for (int chunk = 0; chunk < BLOCK_N / 32; chunk++)
 				{
-					uint32_t r[32];
+					uint32_t r[32], r_second[32];
 					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(chunk * 32), r);
+					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(BLOCK_N + chunk * 32), r_second);
 					umma::tmem_load_wait();
+#pragma unroll
+					for (int q = 0; q < 32; q++)
+						r[q] = __float_as_uint(__uint_as_float(r[q]) + __uint_as_float(r_second[q])); /* (hi*hi + lo*hi) + hi*lo */
 					uint8_t *row_ptr = smem_c + chunk * (kBlockM * 128) + row * 128;
 #pragma unroll
 					for (int j = 0; j < 8; j++)
@@ -464,7 +466,7 @@ namespace
 		}
 		if (warp == 1)
 		{
-			umma::tmem_alloc(&tmem_base_slot, kTnBlockN);
+			umma::tmem_alloc(&tmem_base_slot, 2 * kTnBlockN); /* [0, N) hi*hi + lo*hi, [N, 2N) hi*lo */
 			umma::tmem_relinquish();
 		}
 		umma::fence_proxy_async_smem();
@@ -517,6 +519,7 @@ namespace
 			if (lane == 0)
 			{
 				constexpr uint32_t idesc = umma::make_instr_desc(umma::kAccumF32, umma::kFormatTF32, umma::kFormatTF32, true, true, kBlockM, kTnBlockN);
+				constexpr uint32_t idesc_wide = umma::make_instr_desc(umma::kAccumF32, umma::kFormatTF32, umma::kFormatTF32, true, true, kBlockM, 2 * kTnBlockN);
 				int stage = 0;
 				uint32_t phase = 0;
 				bool ok = true;
@@ -537,11 +540,12 @@ namespace
 						const uint32_t step = static_cast<uint32_t>(k * 1024);
 						const uint64_t a_hi = umma::make_smem_desc(base + step, kTnBlockBytes, 512, umma::kSwizzle128BBase32B);
 						const uint64_t a_lo = umma::make_smem_desc(base + a_lo_offset + step, kTnBlockBytes, 512, umma::kSwizzle128BBase32B);
+						/* the column blocks of B_lo follow those of B_hi at the same 4096-byte pitch: one descriptor with twice the
+						 * width reads both (see the (N,T) kernel: two MMAs and fewer operand reads per slice instead of three) */
 						const uint64_t b_hi = umma::make_smem_desc(base + b_hi_offset + step, kTnBlockBytes, 512, umma::kSwizzle128BBase32B);
-						const uint64_t b_lo = umma::make_smem_desc(base + b_lo_offset + step, kTnBlockBytes, 512, umma::kSwizzle128BBase32B);
-						umma::mma_tf32(tmem_base, a_lo, b_hi, idesc, (kb != kb_begin) or (k != 0));
-						umma::mma_tf32(tmem_base, a_hi, b_lo, idesc, true);
-						umma::mma_tf32(tmem_base, a_hi, b_hi, idesc, true);
+						static_assert(b_lo_offset == b_hi_offset + (kTnBlockN / 32) * kTnBlockBytes, "B_lo must follow B_hi");
+						umma::mma_tf32(tmem_base, a_hi, b_hi, idesc_wide, (kb != kb_begin) or (k != 0));
+						umma::mma_tf32(tmem_base, a_lo, b_hi, idesc, true);
 					}
 					umma::mma_commit(&empty_bar[stage]);
 					if (++stage == kTnStages)
@@ -581,19 +585,9 @@ namespace
 				uint4 *b_hi = a_hi + b_hi_offset / 16;
 				uint4 *b_lo = a_hi + b_lo_offset / 16;
 				for (int i = split_thread; i < a_chunks; i += kSplitThreads)
-				{
-					uint4 hi, lo;
-					split4(a_hi[i], hi, lo);
-					a_hi[i] = hi;
-					a_lo[i] = lo;
-				}
+					a_lo[i] = remainder4(a_hi[i]);
 				for (int i = split_thread; i < b_chunks; i += kSplitThreads)
-				{
-					uint4 hi, lo;
-					split4(b_hi[i], hi, lo);
-					b_hi[i] = hi;
-					b_lo[i] = lo;
-				}
+					b_lo[i] = remainder4(b_hi[i]);
 				umma::fence_proxy_async_smem();
 				umma::mbar_arrive(&split_bar[stage]);
 				if (++stage == kTnStages)
@@ -627,9 +621,13 @@ namespace
 #pragma unroll
 			for (int chunk = 0; chunk < 2; chunk++)
 			{
-				uint32_t r[32];
+				uint32_t r[32], r_second[32];
 				umma::tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(first_column + chunk * 32), r);
+				umma::tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(kTnBlockN + first_column + chunk * 32), r_second);
 				umma::tmem_load_wait();
+#pragma unroll
+				for (int q = 0; q < 32; q++)
+					r[q] = __float_as_uint(__uint_as_float(r[q]) + __uint_as_float(r_second[q])); /* (hi*hi + lo*hi) + hi*lo */
 #pragma unroll
 				for (int j = 0; j < 8; j++)
 				{
@@ -648,7 +646,7 @@ namespace
 		if (warp == 1)
 		{
 			umma::tcgen05_fence_after();
-			umma::tmem_dealloc(tmem_base, kTnBlockN);
+			umma::tmem_dealloc(tmem_base, 2 * kTnBlockN);
 		}
 	}
 
