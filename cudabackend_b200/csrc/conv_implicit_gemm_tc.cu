@@ -746,6 +746,7 @@ namespace
 			{
 				constexpr uint32_t idesc = umma::make_instr_desc(Element<T>::kAccum, Element<T>::kFormat, Element<T>::kFormat, false, false, 2 * kBlockM,
 						kPairBlockN);
+				const uint64_t a_desc0 = umma::make_smem_desc(umma::smem_u32(smem), 16, 1024, umma::kSwizzle128B);
 				int stage = 0;
 				uint32_t phase = 0;
 				int it = 0;
@@ -770,18 +771,13 @@ namespace
 							break;
 						}
 						umma::tcgen05_fence_after();
-						const uint32_t a_addr = umma::smem_u32(smem + stage * Cfg::kStageBytes);
-						const uint32_t b_addr = a_addr + Cfg::kABytes;
-						const uint64_t a_desc = umma::make_smem_desc(a_addr, 16, 1024, umma::kSwizzle128B);
-						const uint64_t b_desc = umma::make_smem_desc(b_addr, 16, 1024, umma::kSwizzle128B);
-#pragma unroll
-						for (int k = 0; k < kElemsPerBlock / kMmaK; k++)
-						{
-							if constexpr (Element<T>::kInteger)
-								umma::mma_i8_pair(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
-							else
-								umma::mma_f16_pair(tmem_d, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0);
-						}
+						const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (Cfg::kStageBytes / 16));
+						const uint64_t b_desc = a_desc + Cfg::kABytes / 16;
+						static_assert(kElemsPerBlock / kMmaK == 4, "a stage is four MMAs deep");
+						if constexpr (Element<T>::kInteger)
+							umma::mma_i8_pair_k4(tmem_d, a_desc, b_desc, idesc, kb != 0);
+						else
+							umma::mma_f16_pair_k4(tmem_d, a_desc, b_desc, idesc, kb != 0);
 						umma::mma_commit_pair(&empty_bar[stage], 3);
 						if (++stage == STAGES)
 						{

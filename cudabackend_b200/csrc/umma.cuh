@@ -339,6 +339,22 @@ namespace umma
 		asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
 				::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate ? 1u : 0u) : "memory");
 	}
+	/* four cta_group::2 MMAs over one 128-byte-wide K-major stage, as mma_*_k4 below do for a single CTA */
+#define B200_UMMA_PAIR_K4(NAME, KIND) \
+	__device__ __forceinline__ void NAME(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, bool accumulateFirst) \
+	{ \
+		asm volatile("{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t" \
+				"setp.ne.b32 p, %4, 0;\n\tsetp.eq.u32 q, %3, %3;\n\t" \
+				"add.s64 a1, %1, 2;\n\tadd.s64 b1, %2, 2;\n\tadd.s64 a2, %1, 4;\n\tadd.s64 b2, %2, 4;\n\tadd.s64 a3, %1, 6;\n\tadd.s64 b3, %2, 6;\n\t" \
+				"tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t" \
+				"tcgen05.mma.cta_group::2.kind::" KIND " [%0], a1, b1, %3, q;\n\t" \
+				"tcgen05.mma.cta_group::2.kind::" KIND " [%0], a2, b2, %3, q;\n\t" \
+				"tcgen05.mma.cta_group::2.kind::" KIND " [%0], a3, b3, %3, q;\n\t}" \
+				::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulateFirst ? 1u : 0u) : "memory"); \
+	}
+	B200_UMMA_PAIR_K4(mma_f16_pair_k4, "f16")
+	B200_UMMA_PAIR_K4(mma_i8_pair_k4, "i8")
+#undef B200_UMMA_PAIR_K4
 	/* one arrival on the mbarrier at this offset in every CTA named by the mask, once all MMAs issued so far are done */
 	__device__ __forceinline__ void mma_commit_pair(uint64_t *bar, uint16_t ctaMask)
 	{
