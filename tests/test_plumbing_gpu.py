@@ -102,3 +102,43 @@ def test_contexts_can_be_ordered_without_blocking_the_host(library, device_count
     graph.destroy()
     side.destroy()
     main.destroy()
+
+
+def test_two_threads_with_their_own_contexts(library, device_count):
+    """Handles, pools and per-device one-time set-up are shared by all threads of a process: two threads, each with its own
+    context and tensors, run convolutions at the same time and must both get the right answer."""
+    if device_count == 0:
+        pytest.skip("no CUDA device visible")
+    import threading
+    from cudabackend_b200 import pipeline
+    from oracle import oracle as o
+    from tests import common
+    failures = []
+
+    def worker(index):
+        try:
+            ctx = api.Context(0)
+            shape = [(3, 12, 14, 64, 72), (2, 17, 9, 40, 64)][index]
+            n, h, w, c, k = shape
+            d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "float16")
+            x = d.x.upload(ctx, common.uniform(["x", "z"][index], d.x.shape))
+            wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+            ref = o.conv2d_forward(x, wt, activation="relu")
+            for repeat in range(25):
+                d.y.mem.zero(ctx)
+                (d.winograd_fused if repeat % 2 else d.implicit_gemm)(activation="relu")
+                err = o.error_metrics(d.y.download(ctx), ref)["elem"]
+                if err > 1e-2:
+                    failures.append((index, repeat, err))
+            if ctx.last_device_status() != 0:
+                failures.append((index, "device status"))
+            ctx.destroy()
+        except Exception as error:  # noqa: BLE001 - reported through the list, the main thread asserts
+            failures.append((index, repr(error)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not failures, failures
