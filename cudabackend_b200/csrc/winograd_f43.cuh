@@ -146,7 +146,8 @@ namespace f43
 	};
 
 	template<int TS, typename T, typename MT>
-	__global__ void __launch_bounds__(kThreads, 3) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
+	/* float32 stages are twice as large, so only two blocks fit an SM anyway: give them the registers of two (no spills) */
+	__global__ void __launch_bounds__(kThreads, sizeof(T) == 4 ? 2 : 3) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
 			int *deviceStatus)
 	{
 		using PT = typename Pair<T>::type;
