@@ -295,7 +295,8 @@ namespace f43
 
 	/* ACT: 0 linear, 1 relu, 2 any (run-time switch) */
 	template<int TS, typename T, typename MT, int ACT>
-	__global__ void __launch_bounds__(kThreads, F43_OUT_BLOCKS) kernel_output(const MT *__restrict__ matrices, T *output, PlaneGeometry g, const float *__restrict__ bias,
+	/* float32 planes need twice the registers for the tile: two resident blocks without spills beat three with them */
+	__global__ void __launch_bounds__(kThreads, sizeof(MT) == 4 ? 2 : F43_OUT_BLOCKS) kernel_output(const MT *__restrict__ matrices, T *output, PlaneGeometry g, const float *__restrict__ bias,
 			const T *__restrict__ ext, float alpha1, float alpha2, float beta, avocado::backend::avActivationType_t activation)
 	{
 		using PT = typename Pair<T>::type;
