@@ -314,13 +314,19 @@ namespace
 #pragma unroll
 				for (int chunk = 0; chunk < BLOCK_N / 32; chunk++)
 				{
-					uint32_t r[32], r_second[32];
+					/* (hi*hi + lo*hi) + hi*lo; the second half is taken 16 columns at a time to keep the live registers down */
+					uint32_t r[32], r_second[16];
 					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(chunk * 32), r);
-					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(BLOCK_N + chunk * 32), r_second);
+					umma::tmem_load_32x16(t_addr + static_cast<uint32_t>(BLOCK_N + chunk * 32), r_second);
 					umma::tmem_load_wait();
 #pragma unroll
-					for (int q = 0; q < 32; q++)
-						r[q] = __float_as_uint(__uint_as_float(r[q]) + __uint_as_float(r_second[q])); /* (hi*hi + lo*hi) + hi*lo */
+					for (int q = 0; q < 16; q++)
+						r[q] = __float_as_uint(__uint_as_float(r[q]) + __uint_as_float(r_second[q]));
+					umma::tmem_load_32x16(t_addr + static_cast<uint32_t>(BLOCK_N + chunk * 32 + 16), r_second);
+					umma::tmem_load_wait();
+#pragma unroll
+					for (int q = 0; q < 16; q++)
+						r[16 + q] = __float_as_uint(__uint_as_float(r[16 + q]) + __uint_as_float(r_second[q]));
 					uint8_t *row_ptr = smem_c + chunk * (kBlockM * 128) + row * 128;
 #pragma unroll
 					for (int j = 0; j < 8; j++)
