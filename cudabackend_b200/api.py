@@ -82,6 +82,7 @@ SIGNATURES = {
     "cudaDestroyCapturedGraph": (_INT, [_I64]),
     "cudaConvolutionWinogradFusedForwardNoAlloc": (_INT, _conv_args),
     "cudaRunBoundedWaitSelfTest": (_INT, [_H, _INT]),
+    "cudaRunBoundedWaitSelfTestNoAlloc": (_INT, [_H, _INT]),
     "cudaContextWaitForContext": (_INT, [_H, _H]),
     "cudaIm2Row": (_INT, [_H, _H, _H, _H, _H, _H, _H]),
     "cudaOptimizerLearn": (_INT, [_H, _H, _VP, _H, _H, _VP, _H, _H, _H]),

@@ -880,12 +880,11 @@ namespace
 	{
 		using Cfg = IgPairConfig<STAGES>;
 		auto kernel = kernel_implicit_gemm_tc_pair<T, STAGES>;
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		p.n_blocks = (p.filters + kPairBlockN - 1) / kPairBlockN;
 		const int m_pairs = (p.pixels + 2 * kBlockM - 1) / (2 * kBlockM);
@@ -905,12 +904,11 @@ namespace
 	{
 		using Cfg = IgConfig<BLOCK_N, STAGES>;
 		auto kernel = kernel_implicit_gemm_tc<T, BLOCK_N, STAGES>;
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		p.n_blocks = (p.filters + BLOCK_N - 1) / BLOCK_N;
 		const long long tiles = static_cast<long long>(p.m_blocks) * p.n_blocks;

@@ -23,6 +23,10 @@ namespace bk
 	/* Contraction + output transform of the F(2x2,3x3) convolution in one kernel: reads V[16][tiles][C] and U[16][K][C]
 	 * (float16), writes y (float16 / bfloat16) with the bias / z / activation / beta epilogue of args.  deviceStatus is
 	 * the word that receives the bit of a wait that ran out. */
+	/* whether the kernel below takes this problem (device, dtype, extents and the alignment of y, z and bias), given
+	 * transform-domain tensors that are 128-byte aligned */
+	bool winograd_f23_contract_output_covers(const avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
+			avocado::backend::avDataType_t yType, long long tiles);
 	avocado::backend::avStatus_t winograd_f23_contract_output(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
 			avocado::backend::avDataType_t yType, long long tiles, const void *vPtr, const void *uPtr, const void *alpha1, const void *alpha2, const void *beta,
 			int *deviceStatus);

@@ -9,6 +9,7 @@
 #include <Avocado/cuda_backend_ext.h>
 
 #include "objects.hpp"
+#include "winograd_internal.hpp"
 
 #include <algorithm>
 #include <cstdio>
@@ -146,6 +147,7 @@ namespace avocado
 			}
 			void* ContextObject::getWorkspace(size_t bytes)
 			{
+				std::lock_guard<std::mutex> lock(lazy_mutex);
 				if (bytes > workspace_size)
 				{
 					setDevice();
@@ -166,6 +168,7 @@ namespace avocado
 			}
 			int* ContextObject::getDeviceStatus()
 			{
+				std::lock_guard<std::mutex> lock(lazy_mutex);
 				if (device_status == nullptr)
 				{
 					setDevice();
@@ -598,7 +601,11 @@ namespace avocado
 					}
 					return convertStatus(status);
 				}
-				/* no peer access: bounce through host memory, as the reference does (src/descriptors.cu:126-135) */
+				/* no peer access: bounce through host memory, as the reference does (src/descriptors.cu:126-135).  The
+				 * context's stream does not synchronise with the legacy stream the blocking copies run on, so wait for
+				 * the kernels that may still be producing the source first. */
+				if (not ctx.is_default and cudaStreamSynchronize(ctx.getStream()) != cudaSuccess)
+					return checkForErrors();
 				std::unique_ptr<uint8_t[]> buffer(new uint8_t[count]);
 				cudaError_t status = cudaMemcpy(buffer.get(), sptr, count, cudaMemcpyDeviceToHost);
 				if (status != cudaSuccess)
@@ -831,18 +838,31 @@ namespace avocado
 			AVOCADO_API_BEGIN
 				ContextObject &ctx = getContext(context);
 				ctx.setDevice();
-				if (ctx.device_status == nullptr)
+				/* two words can hold a report: the context's own, and the one inside the fixed scratch array of the
+				 * entry point that allocates nothing (shared by every context of the device) */
+				int *words[2] = { ctx.device_status, bk::no_alloc_status_word(ctx.device) };
+				if (words[0] == nullptr and words[1] == nullptr)
 				{
 					result[0] = 0;
 					return AVOCADO_STATUS_SUCCESS;
 				}
 				if (cudaStreamSynchronize(ctx.getStream()) != cudaSuccess)
 					return AVOCADO_STATUS_EXECUTION_FAILED;
-				int value = 0;
-				if (cudaMemcpy(&value, ctx.device_status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
-					return AVOCADO_STATUS_EXECUTION_FAILED;
-				cudaMemset(ctx.device_status, 0, sizeof(int));
-				result[0] = value;
+				int combined = 0;
+				for (int *word : words)
+				{
+					if (word == nullptr)
+						continue;
+					int value = 0;
+					if (cudaMemcpyAsync(&value, word, sizeof(int), cudaMemcpyDeviceToHost, ctx.getStream()) != cudaSuccess
+							or cudaStreamSynchronize(ctx.getStream()) != cudaSuccess)
+						return AVOCADO_STATUS_EXECUTION_FAILED;
+					/* cleared on the context's own stream, so the clear is ordered before the next kernel of this context */
+					if (value != 0 and cudaMemsetAsync(word, 0, sizeof(int), ctx.getStream()) != cudaSuccess)
+						return AVOCADO_STATUS_EXECUTION_FAILED;
+					combined |= value;
+				}
+				result[0] = combined;
 				return AVOCADO_STATUS_SUCCESS;
 			AVOCADO_API_END
 		}

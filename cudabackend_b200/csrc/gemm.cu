@@ -456,12 +456,11 @@ namespace
 	{
 		using Cfg = TcConfig<BLOCK_N, STAGES, EPI_BUFS>;
 		auto kernel = kernel_gemm_nt_tc<BLOCK_N, STAGES, EPI_BUFS, IS_BF16>;
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		const int mBlocks = (s.M + kBlockM - 1) / kBlockM;
 		const int nBlocks = (s.N + BLOCK_N - 1) / BLOCK_N;
@@ -648,19 +647,30 @@ namespace avocado
 {
 	namespace backend
 	{
-		avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, int limitMicroseconds)
+		static avStatus_t run_bounded_wait_selftest(avContextDescriptor_t context, int limitMicroseconds, bool noAllocWord)
 		{
 			if (limitMicroseconds < 1 or limitMicroseconds > 1000000)
 				return AVOCADO_STATUS_BAD_PARAM;
 			AVOCADO_API_BEGIN
 				ContextObject &ctx = getContext(context);
 				ctx.setDevice();
+				int *word = noAllocWord ? bk::no_alloc_status_word(ctx.device) : ctx.getDeviceStatus();
+				if (word == nullptr)
+					return AVOCADO_STATUS_BAD_PARAM; /* the fixed array has not been used on this device yet */
 				int khz = 0;
 				cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx.device);
 				const long long cycles = static_cast<long long>(limitMicroseconds) * std::max(khz, 1000) / 1000;
-				kernel_bounded_wait_selftest<<<1, 32, 0, ctx.getStream()>>>(cycles, ctx.getDeviceStatus());
+				kernel_bounded_wait_selftest<<<1, 32, 0, ctx.getStream()>>>(cycles, word);
 				return checkForErrors();
 			AVOCADO_API_END
+		}
+		avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, int limitMicroseconds)
+		{
+			return run_bounded_wait_selftest(context, limitMicroseconds, false);
+		}
+		avStatus_t cudaRunBoundedWaitSelfTestNoAlloc(avContextDescriptor_t context, int limitMicroseconds)
+		{
+			return run_bounded_wait_selftest(context, limitMicroseconds, true);
 		}
 	}
 }

@@ -719,13 +719,11 @@ namespace
 		const size_t partial_bytes = static_cast<size_t>(splits) * tiles * kBlockM * kTnBlockN * sizeof(float);
 		float *partial = reinterpret_cast<float*>(ctx.getWorkspace(partial_bytes));
 
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { { const cudaError_t e = cudaFuncSetAttribute(kernel_gemm_tn_tf32x3<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TnLayout<false>::kSmemBytes); if (e != cudaSuccess) return e; } return cudaFuncSetAttribute(kernel_gemm_tn_tf32x3<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TnLayout<true>::kSmemBytes); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel_gemm_tn_tf32x3<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TnLayout<false>::kSmemBytes) != cudaSuccess
-					or cudaFuncSetAttribute(kernel_gemm_tn_tf32x3<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TnLayout<true>::kSmemBytes) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		const dim3 grid(splits, static_cast<unsigned int>(grid_tiles));
 		if (paired)
@@ -750,12 +748,11 @@ namespace
 	{
 		using Cfg = Config<BLOCK_N, STAGES>;
 		auto kernel = kernel_gemm_nt_tf32x3<BLOCK_N, STAGES>;
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		const int mBlocks = (s.M + kBlockM - 1) / kBlockM;
 		const int nBlocks = (s.N + BLOCK_N - 1) / BLOCK_N;

@@ -37,6 +37,24 @@ namespace avocado
 
 			constexpr int kMaxDevices = 64;
 
+			/* One-time set-up per device (kernel attributes and the like) that several host threads may reach at the
+			 * same moment: the first caller on a device runs `configure`, the others wait for it and see its result. */
+			class PerDeviceOnce
+			{
+					std::once_flag m_flags[kMaxDevices];
+					cudaError_t m_results[kMaxDevices] = { };
+				public:
+					template<class F>
+					cudaError_t run(int device, F &&configure)
+					{
+						if (device < 0 or device >= kMaxDevices)
+							return cudaErrorInvalidDevice;
+						std::call_once(m_flags[device], [&]()
+						{	m_results[device] = configure();});
+						return m_results[device];
+					}
+			};
+
 			inline int64_t make_handle(Kind kind, bool isDefault, uint32_t generation, uint32_t slot) noexcept
 			{
 				return (static_cast<int64_t>(kind) << 56) | (static_cast<int64_t>(isDefault ? 1 : 0) << 55)
@@ -162,6 +180,7 @@ namespace avocado
 				size_t workspace_size = 0;
 				int *device_status = nullptr;
 				cudaEvent_t order_event = nullptr; /* recorded on this stream when another context waits for this one */
+				std::mutex lazy_mutex; /* guards the first allocation of workspace and device_status */
 
 				explicit ContextObject(int deviceIndex, bool isDefault);
 				~ContextObject();

@@ -26,63 +26,119 @@ namespace f43
 {
 	using namespace bk;
 
-	__device__ __forceinline__ void input_1d(const float (&d)[6], float (&o)[6])
+	/* Two float32 values in one 64-bit register pair, operated on by the packed FP32 instructions of sm_100
+	 * (add / sub / mul / fma .f32x2): one instruction per two channels.  Every operation rounds each half exactly like
+	 * its scalar counterpart, so the transforms below give bit for bit what the scalar formulas give. */
+	struct f2
 	{
-		const float c = d[4] - d[2];
-		const float e = d[3] - d[1];
-		const float a = fmaf(-0.25f, d[4], d[2]);
-		const float b = fmaf(-0.25f, d[3], d[1]);
-		o[0] = fmaf(0.25f, c, d[0] - d[2]);
-		o[1] = a + b;
-		o[2] = a - b;
-		o[3] = fmaf(0.5f, c, e);
-		o[4] = fmaf(0.5f, c, -e);
-		o[5] = fmaf(0.25f, d[5] - d[3], -e);
+			unsigned long long v;
+	};
+	__device__ __forceinline__ f2 make_f2(float a, float b)
+	{
+		f2 r;
+		asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b));
+		return r;
 	}
-	__device__ __forceinline__ void output_1d(const float (&m)[6], float (&o)[4])
+	__device__ __forceinline__ f2 make_f2(float2 a)
 	{
-		const float s = m[1] + m[2];
-		const float d = m[1] - m[2];
-		const float u = m[3] + m[4];
-		const float v = m[3] - m[4];
-		o[0] = fmaf(0.25f, u, m[0] + s);
-		o[1] = fmaf(0.5f, v, d);
-		o[2] = s + u;
-		o[3] = fmaf(2.0f, v + m[5], d);
+		return make_f2(a.x, a.y);
 	}
-	__device__ __forceinline__ void gradient_1d(const float (&g)[4], float (&o)[6])
+	__device__ __forceinline__ f2 splat(float a)
 	{
-		constexpr float k13 = 1.0f / 3.0f, k23 = 2.0f / 3.0f, k43 = 4.0f / 3.0f, k83 = 8.0f / 3.0f;
-		const float s = g[0] + g[2];
-		const float t = g[1] + g[3];
-		const float p = fmaf(k43, g[2], k13 * g[0]);
-		const float q = fmaf(k83, g[3], k23 * g[1]);
+		return make_f2(a, a);
+	}
+	__device__ __forceinline__ float2 to_float2(f2 a)
+	{
+		float2 r;
+		asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(a.v));
+		return r;
+	}
+	__device__ __forceinline__ f2 add2(f2 a, f2 b)
+	{
+		f2 r;
+		asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+		return r;
+	}
+	__device__ __forceinline__ f2 sub2(f2 a, f2 b)
+	{
+		f2 r;
+		asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+		return r;
+	}
+	__device__ __forceinline__ f2 mul2(f2 a, f2 b)
+	{
+		f2 r;
+		asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+		return r;
+	}
+	__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) /* a * b + c, one rounding */
+	{
+		f2 r;
+		asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+		return r;
+	}
+
+	__device__ __forceinline__ void input_1d(const f2 (&d)[6], f2 (&o)[6])
+	{
+		const f2 quarter = splat(0.25f), half_ = splat(0.5f), minus_quarter = splat(-0.25f);
+		const f2 c = sub2(d[4], d[2]);
+		const f2 e = sub2(d[3], d[1]);
+		const f2 minus_e = sub2(d[1], d[3]); /* exactly -e */
+		const f2 a = fma2(minus_quarter, d[4], d[2]);
+		const f2 b = fma2(minus_quarter, d[3], d[1]);
+		o[0] = fma2(quarter, c, sub2(d[0], d[2]));
+		o[1] = add2(a, b);
+		o[2] = sub2(a, b);
+		o[3] = fma2(half_, c, e);
+		o[4] = fma2(half_, c, minus_e);
+		o[5] = fma2(quarter, sub2(d[5], d[3]), minus_e);
+	}
+	__device__ __forceinline__ void output_1d(const f2 (&m)[6], f2 (&o)[4])
+	{
+		const f2 quarter = splat(0.25f), half_ = splat(0.5f), two = splat(2.0f);
+		const f2 s = add2(m[1], m[2]);
+		const f2 d = sub2(m[1], m[2]);
+		const f2 u = add2(m[3], m[4]);
+		const f2 v = sub2(m[3], m[4]);
+		o[0] = fma2(quarter, u, add2(m[0], s));
+		o[1] = fma2(half_, v, d);
+		o[2] = add2(s, u);
+		o[3] = fma2(two, add2(v, m[5]), d);
+	}
+	__device__ __forceinline__ void gradient_1d(const f2 (&g)[4], f2 (&o)[6])
+	{
+		const f2 k13 = splat(1.0f / 3.0f), k23 = splat(2.0f / 3.0f), k43 = splat(4.0f / 3.0f), k83 = splat(8.0f / 3.0f), two = splat(2.0f);
+		const f2 s = add2(g[0], g[2]);
+		const f2 t = add2(g[1], g[3]);
+		const f2 p = fma2(k43, g[2], mul2(k13, g[0]));
+		const f2 q = fma2(k83, g[3], mul2(k23, g[1]));
 		o[0] = g[0];
-		o[1] = k23 * (s + t);
-		o[2] = k23 * (s - t);
-		o[3] = p + q;
-		o[4] = p - q;
-		o[5] = 2.0f * g[3];
+		o[1] = mul2(k23, add2(s, t));
+		o[2] = mul2(k23, sub2(s, t));
+		o[3] = add2(p, q);
+		o[4] = sub2(p, q);
+		o[5] = mul2(two, g[3]);
 	}
 
 	/* F(2x2,3x3) one-dimensional transforms (reference tables src/winograd_nonfused.cu:534-539) */
-	__device__ __forceinline__ void input_1d(const float (&d)[4], float (&o)[4])
+	__device__ __forceinline__ void input_1d(const f2 (&d)[4], f2 (&o)[4])
 	{
-		o[0] = d[0] - d[2];
-		o[1] = d[1] + d[2];
-		o[2] = d[2] - d[1];
-		o[3] = d[3] - d[1];
+		o[0] = sub2(d[0], d[2]);
+		o[1] = add2(d[1], d[2]);
+		o[2] = sub2(d[2], d[1]);
+		o[3] = sub2(d[3], d[1]);
 	}
-	__device__ __forceinline__ void output_1d(const float (&m)[4], float (&o)[2])
+	__device__ __forceinline__ void output_1d(const f2 (&m)[4], f2 (&o)[2])
 	{
-		o[0] = fmaf(0.5f, m[1] + m[2], m[0]);
-		o[1] = fmaf(0.5f, m[1] - m[2], m[3]);
+		const f2 half_ = splat(0.5f);
+		o[0] = fma2(half_, add2(m[1], m[2]), m[0]);
+		o[1] = fma2(half_, sub2(m[1], m[2]), m[3]);
 	}
-	__device__ __forceinline__ void gradient_1d(const float (&g)[2], float (&o)[4])
+	__device__ __forceinline__ void gradient_1d(const f2 (&g)[2], f2 (&o)[4])
 	{
 		o[0] = g[0];
-		o[1] = g[0] + g[1];
-		o[2] = g[0] - g[1];
+		o[1] = add2(g[0], g[1]);
+		o[2] = sub2(g[0], g[1]);
 		o[3] = g[1];
 	}
 
@@ -125,6 +181,35 @@ namespace f43
 			}
 	};
 
+	template<typename T>
+	__device__ __forceinline__ f2 load_pair(const T *ptr) /* two adjacent channels, converted to float32 */
+	{
+		return make_f2(Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::type*>(ptr)));
+	}
+	template<>
+	__device__ __forceinline__ f2 load_pair<float>(const float *ptr)
+	{
+		f2 r;
+		r.v = *reinterpret_cast<const unsigned long long*>(ptr);
+		return r;
+	}
+	template<typename T>
+	__device__ __forceinline__ f2 unpack_pair(typename Pair<T>::type raw)
+	{
+		return make_f2(Pair<T>::unpack(raw));
+	}
+	template<typename T>
+	__device__ __forceinline__ void store_pair(T *ptr, f2 value) /* rounded once, to nearest even */
+	{
+		const float2 v = to_float2(value);
+		*reinterpret_cast<typename Pair<T>::type*>(ptr) = Pair<T>::pack(v.x, v.y);
+	}
+	template<>
+	__device__ __forceinline__ void store_pair<float>(float *ptr, f2 value)
+	{
+		*reinterpret_cast<unsigned long long*>(ptr) = value.v;
+	}
+
 	constexpr int kChannelBlock = 64; /* channels per strip: one warp, two channels per lane */
 	constexpr int kThreads = 256;
 	constexpr int kMaxStages = 4;
@@ -146,8 +231,8 @@ namespace f43
 	};
 
 	template<int TS, typename T, typename MT>
-	/* float32 stages are twice as large, so only two blocks fit an SM anyway: give them the registers of two (no spills) */
-	__global__ void __launch_bounds__(kThreads, sizeof(T) == 4 ? 2 : 3) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
+	/* the halo ring (up to 96 KB per block) lets two blocks share an SM: give each the registers of half an SM (no spills) */
+	__global__ void __launch_bounds__(kThreads, 2) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
 			int *deviceStatus)
 	{
 		using PT = typename Pair<T>::type;
@@ -236,46 +321,33 @@ namespace f43
 				constexpr int TL = TS + 2;
 				const T *src = box + (tr * TS) * row_pitch + (tc * TS) * kChannelBlock + 2 * lane;
 
-				float tmp[2][TL * TL]; /* B^T d, per channel */
+				f2 tmp[TL * TL]; /* B^T d, both channels of the lane */
 #pragma unroll
 				for (int c = 0; c < TL; c++)
 				{
-					float col0[TL], col1[TL];
+					f2 col[TL], o[TL];
 #pragma unroll
 					for (int r = 0; r < TL; r++)
-					{
-						const float2 v = Pair<T>::unpack(*reinterpret_cast<const PT*>(src + r * row_pitch + c * kChannelBlock));
-						col0[r] = v.x;
-						col1[r] = v.y;
-					}
-					float o0[TL], o1[TL];
-					input_1d(col0, o0);
-					input_1d(col1, o1);
+						col[r] = load_pair<T>(src + r * row_pitch + c * kChannelBlock);
+					input_1d(col, o);
 #pragma unroll
 					for (int i = 0; i < TL; i++)
-					{
-						tmp[0][i * TL + c] = o0[i];
-						tmp[1][i * TL + c] = o1[i];
-					}
+						tmp[i * TL + c] = o[i];
 				}
 				const long long tile = (static_cast<long long>(n) * g.tiles_h + th) * g.tiles_w + tw;
 				MT *dst = matrices + static_cast<size_t>(tile) * g.channels + c0;
 #pragma unroll
 				for (int i = 0; i < TL; i++)
 				{
-					float row0[TL], row1[TL], o0[TL], o1[TL];
+					f2 row[TL], o[TL];
 #pragma unroll
 					for (int c = 0; c < TL; c++)
-					{
-						row0[c] = tmp[0][i * TL + c];
-						row1[c] = tmp[1][i * TL + c];
-					}
-					input_1d(row0, o0);
-					input_1d(row1, o1);
+						row[c] = tmp[i * TL + c];
+					input_1d(row, o);
 #pragma unroll
 					for (int j = 0; j < TL; j++)
 					{
-						*reinterpret_cast<PM*>(dst) = Pair<MT>::pack(o0[j], o1[j]);
+						store_pair<MT>(dst, o[j]);
 						dst += plane_stride;
 					}
 				}
@@ -323,30 +395,23 @@ namespace f43
 			raw[p] = *reinterpret_cast<const PM*>(src);
 			src += plane_stride;
 		}
-		float tmp[2][TS * TL]; /* A^T M: TS x TL per channel */
+		f2 tmp[TS * TL]; /* A^T M: TS x TL, both channels of the lane */
 #pragma unroll
 		for (int c = 0; c < TL; c++)
 		{
-			float col0[TL], col1[TL], o0[TS], o1[TS];
+			f2 col[TL], o[TS];
 #pragma unroll
 			for (int r = 0; r < TL; r++)
-			{
-				const float2 v = Pair<MT>::unpack(raw[r * TL + c]);
-				col0[r] = v.x;
-				col1[r] = v.y;
-			}
-			output_1d(col0, o0);
-			output_1d(col1, o1);
+				col[r] = unpack_pair<MT>(raw[r * TL + c]);
+			output_1d(col, o);
 #pragma unroll
 			for (int i = 0; i < TS; i++)
-			{
-				tmp[0][i * TL + c] = o0[i];
-				tmp[1][i * TL + c] = o1[i];
-			}
+				tmp[i * TL + c] = o[i];
 		}
-		float2 b = make_float2(0.0f, 0.0f);
+		f2 b = splat(0.0f);
 		if (bias != nullptr)
-			b = *reinterpret_cast<const float2*>(bias + c0);
+			b = load_pair<float>(bias + c0);
+		const f2 a1 = splat(alpha1), a2 = splat(alpha2), bt = splat(beta), zero = splat(0.0f);
 
 		const int h0 = th * TS, w0 = tw * TS;
 		T *tile_ptr = output + ((static_cast<size_t>(n) * g.height + h0) * g.width + w0) * g.channels + c0;
@@ -356,49 +421,38 @@ namespace f43
 #pragma unroll
 		for (int i = 0; i < TS; i++)
 		{
-			float row0[TL], row1[TL], o0[TS], o1[TS];
+			f2 row[TL], o[TS];
 #pragma unroll
 			for (int c = 0; c < TL; c++)
-			{
-				row0[c] = tmp[0][i * TL + c];
-				row1[c] = tmp[1][i * TL + c];
-			}
-			output_1d(row0, o0);
-			output_1d(row1, o1);
+				row[c] = tmp[i * TL + c];
+			output_1d(row, o);
 #pragma unroll
 			for (int j = 0; j < TS; j++)
 			{
 				if (interior or (h0 + i < g.height and w0 + j < g.width))
 				{
 					const int offset = i * row_stride + j * g.channels;
-					float v0 = fmaf(alpha1, o0[j], b.x);
-					float v1 = fmaf(alpha1, o1[j], b.y);
+					f2 v = fma2(a1, o[j], b);
 					if (ext_ptr != nullptr)
-					{
-						const float2 z = Pair<T>::unpack(*reinterpret_cast<const PT*>(ext_ptr + offset));
-						v0 = fmaf(alpha2, z.x, v0);
-						v1 = fmaf(alpha2, z.y, v1);
-					}
+						v = fma2(a2, load_pair<T>(ext_ptr + offset), v);
 					if (ACT == 1)
 					{
-						v0 = fmaxf(v0, 0.0f);
-						v1 = fmaxf(v1, 0.0f);
+						/* relu as the scalar fmaxf(v, 0) of each half (no packed maximum exists) */
+						const float2 u = to_float2(v);
+						v = make_f2(fmaxf(u.x, 0.0f), fmaxf(u.y, 0.0f));
 					}
 					else if (ACT == 2)
 					{
-						v0 = activation_forward(activation, v0);
-						v1 = activation_forward(activation, v1);
+						const float2 u = to_float2(v);
+						v = make_f2(activation_forward(activation, u.x), activation_forward(activation, u.y));
 					}
 					if (beta != 0.0f)
-					{
-						const float2 y = Pair<T>::unpack(*reinterpret_cast<const PT*>(tile_ptr + offset));
-						v0 = fmaf(beta, y.x, v0);
-						v1 = fmaf(beta, y.y, v1);
-					}
-					*reinterpret_cast<PT*>(tile_ptr + offset) = Pair<T>::pack(v0, v1);
+						v = fma2(bt, load_pair<T>(tile_ptr + offset), v);
+					store_pair<T>(tile_ptr + offset, v);
 				}
 			}
 		}
+		(void) zero;
 	}
 
 	/* dy[N,H,W,K] -> [tile*tile, tiles, K]: TS x TS tile, zero past the image edge (reference src/winograd_nonfused.cu:424-475) */
@@ -435,45 +489,33 @@ namespace f43
 				else
 					raw[r * TS + c] = Pair<T>::pack(0.0f, 0.0f);
 			}
-		float tmp[2][TL * TS]; /* G' g: TL x TS per channel */
+		f2 tmp[TL * TS]; /* G' g: TL x TS, both channels of the lane */
 #pragma unroll
 		for (int c = 0; c < TS; c++)
 		{
-			float col0[TS], col1[TS], o0[TL], o1[TL];
+			f2 col[TS], o[TL];
 #pragma unroll
 			for (int r = 0; r < TS; r++)
-			{
-				const float2 v = Pair<T>::unpack(raw[r * TS + c]);
-				col0[r] = v.x;
-				col1[r] = v.y;
-			}
-			gradient_1d(col0, o0);
-			gradient_1d(col1, o1);
+				col[r] = unpack_pair<T>(raw[r * TS + c]);
+			gradient_1d(col, o);
 #pragma unroll
 			for (int i = 0; i < TL; i++)
-			{
-				tmp[0][i * TS + c] = o0[i];
-				tmp[1][i * TS + c] = o1[i];
-			}
+				tmp[i * TS + c] = o[i];
 		}
 		const size_t plane_stride = static_cast<size_t>(g.nb_tiles) * g.channels;
 		MT *dst = matrices + static_cast<size_t>(tile) * g.channels + c0;
 #pragma unroll
 		for (int i = 0; i < TL; i++)
 		{
-			float row0[TS], row1[TS], o0[TL], o1[TL];
+			f2 row[TS], o[TL];
 #pragma unroll
 			for (int c = 0; c < TS; c++)
-			{
-				row0[c] = tmp[0][i * TS + c];
-				row1[c] = tmp[1][i * TS + c];
-			}
-			gradient_1d(row0, o0);
-			gradient_1d(row1, o1);
+				row[c] = tmp[i * TS + c];
+			gradient_1d(row, o);
 #pragma unroll
 			for (int j = 0; j < TL; j++)
 			{
-				*reinterpret_cast<PM*>(dst) = Pair<MT>::pack(o0[j], o1[j]);
+				store_pair<MT>(dst, o[j]);
 				dst += plane_stride;
 			}
 		}

@@ -475,13 +475,11 @@ namespace
 	{
 		const bool simple = p.z == nullptr and p.beta == 0.0f and (p.activation == AVOCADO_ACTIVATION_LINEAR or p.activation == AVOCADO_ACTIVATION_RELU);
 		auto kernel = simple ? kernel_f23_contract_output<T, true> : kernel_f23_contract_output<T, false>;
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { { const cudaError_t e = cudaFuncSetAttribute(kernel_f23_contract_output<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes); if (e != cudaSuccess) return e; } return cudaFuncSetAttribute(kernel_f23_contract_output<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel_f23_contract_output<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess
-					or cudaFuncSetAttribute(kernel_f23_contract_output<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
@@ -493,18 +491,25 @@ namespace
 
 namespace bk
 {
+	bool winograd_f23_contract_output_covers(const ContextObject &ctx, const ConvArgs &args, avDataType_t yType, long long tiles)
+	{
+		if (cuda_sm_version(ctx.device) != 100)
+			return false;
+		if (yType != AVOCADO_DTYPE_FLOAT16 and yType != AVOCADO_DTYPE_BFLOAT16)
+			return false;
+		/* rows of V and U must be whole 16-byte units for TMA, outputs are stored 8 filters at a time */
+		if (args.channels % 8 != 0 or args.filters % 8 != 0 or tiles > 0x7FFFFF00ll)
+			return false;
+		return reinterpret_cast<uintptr_t>(args.y) % 16 == 0 and (args.z == nullptr or reinterpret_cast<uintptr_t>(args.z) % 16 == 0)
+				and (args.bias == nullptr or reinterpret_cast<uintptr_t>(args.bias) % 4 == 0);
+	}
+
 	avStatus_t winograd_f23_contract_output(ContextObject &ctx, const ConvArgs &args, avDataType_t yType, long long tiles, const void *vPtr, const void *uPtr,
 			const void *alpha1, const void *alpha2, const void *beta, int *deviceStatus)
 	{
-		if (cuda_sm_version(ctx.device) != 100)
+		if (not winograd_f23_contract_output_covers(ctx, args, yType, tiles))
 			return AVOCADO_STATUS_NOT_SUPPORTED;
-		if (yType != AVOCADO_DTYPE_FLOAT16 and yType != AVOCADO_DTYPE_BFLOAT16)
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		/* rows of V and U must be whole 16-byte units for TMA, outputs are stored 8 filters at a time */
-		if (args.channels % 8 != 0 or args.filters % 8 != 0 or tiles > 0x7FFFFF00ll)
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		if (reinterpret_cast<uintptr_t>(vPtr) % 128 != 0 or reinterpret_cast<uintptr_t>(uPtr) % 128 != 0 or reinterpret_cast<uintptr_t>(args.y) % 16 != 0
-				or (args.z != nullptr and reinterpret_cast<uintptr_t>(args.z) % 16 != 0) or (args.bias != nullptr and reinterpret_cast<uintptr_t>(args.bias) % 4 != 0))
+		if (reinterpret_cast<uintptr_t>(vPtr) % 128 != 0 or reinterpret_cast<uintptr_t>(uPtr) % 128 != 0)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 
 		CUtensorMap mapV, mapU;

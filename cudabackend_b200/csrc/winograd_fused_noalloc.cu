@@ -7,21 +7,30 @@
  * tolerate that: an inference server that has handed the whole GPU to its own memory pool has nothing left for
  * cudaMalloc to return; a latency-bound control loop cannot absorb the device-wide synchronisation an allocation
  * implies; a process running under a "no allocation after start-up" policy is simply not allowed to.  For them the
- * scratch lives in the library image itself: a file-scope __device__ array, reserved on every GPU that loads the
- * library for as long as the process lives, and limited to AVOCADO_NO_ALLOC_SCRATCH_BYTES.
+ * scratch lives in the library image itself: a file-scope __device__ array, part of the library's device code on
+ * every GPU that uses it for as long as the process lives, and limited to AVOCADO_NO_ALLOC_SCRATCH_BYTES.
  *
  * What it computes: exactly what cudaConvolutionWinogradFusedForward computes for float16 and bfloat16 tensors with a
- * 3x3 kernel (same kernels, same order, bit-identical result), as long as the three transform-domain tensors fit:
- *     16 * 2 bytes * (K*C + tiles*C + tiles*K) <= AVOCADO_NO_ALLOC_SCRATCH_BYTES,   tiles = N * ceil(H/2) * ceil(W/2)
- * A larger problem is refused with AVOCADO_STATUS_BAD_PARAM before anything is launched.
+ * 3x3 kernel (same kernels, same order, bit-identical result), as long as the transform-domain tensors fit:
+ *     32 * (K*C + tiles*C) bytes <= AVOCADO_NO_ALLOC_SCRATCH_BYTES,   tiles = N * ceil(H/2) * ceil(W/2)
+ * (each term rounded up to 256 bytes).  When y, z or the bias is not aligned to 16 / 16 / 4 bytes the single-kernel
+ * contraction + output transform does not apply and the products M are written out as well, which adds 32 * tiles*K
+ * bytes to the sum.  A problem that does not fit is refused with AVOCADO_STATUS_BAD_PARAM before anything is
+ * launched.  Where the allocating entry point would fall back to CUDA-core kernels (C or K not a multiple of 8) this
+ * one returns AVOCADO_STATUS_NOT_SUPPORTED: those kernels are outside the no-allocation guarantee.
  *
  * Rules for the caller:
  *  - The first call on each device looks up the device address of the array (cudaGetSymbolAddress with that device
- *    current) and sets the kernels' shared-memory attributes.  Make that first call before any stream capture.
+ *    current) and sets the kernels' shared-memory attributes.  The CUDA runtime loads device code lazily, so this
+ *    first call is also the moment the driver places the array (and the kernels) in device memory, and it
+ *    synchronises.  Make it during start-up: before the host's own pool takes the remaining memory and before any
+ *    stream capture.  (CUDA_MODULE_LOADING=EAGER moves the loading to library load time instead.)
  *  - All calls on a device share the one array, whatever context they use.  Two calls whose work overlaps on the
  *    GPU (different streams, no ordering between them) race on it; order them or use the allocating entry point.
  *  - The array keeps the previous call's contents.  Nothing needs to start from zero except the 256-byte word in
- *    which the tensor-core kernel reports a wait that ran out; each call clears it on its stream first.
+ *    which the tensor-core kernels report a wait that ran out.  That word starts as zero (static initialisation),
+ *    is only ever OR-ed into by kernels, and is read and cleared by cudaGetLastDeviceStatus of any context on the
+ *    device -- a report is therefore kept until somebody reads it.
  *  - No cudaMalloc, cudaFree or allocating library routine is called on this path.
  */
 #include <Avocado/cuda_backend.h>
@@ -45,14 +54,15 @@ namespace
 	 * In host code this name is only a stand-in for the symbol, never a device address. */
 	static __device__ __align__(256) unsigned char no_alloc_scratch[kStatusBytes + kScratchBytes];
 
+	std::mutex address_mutex;
+	unsigned char *address[kMaxDevices] = { };
+
 	/* device address of the array, looked up once per device with that device current */
 	avStatus_t scratch_address(int device, unsigned char **result)
 	{
-		static std::mutex mutex;
-		static unsigned char *address[kMaxDevices] = { };
 		if (device < 0 or device >= kMaxDevices)
 			return AVOCADO_STATUS_BAD_PARAM;
-		std::lock_guard<std::mutex> lock(mutex);
+		std::lock_guard<std::mutex> lock(address_mutex);
 		if (address[device] == nullptr)
 		{
 			if (cudaSetDevice(device) != cudaSuccess)
@@ -85,6 +95,17 @@ namespace
 		return t;
 	}
 }
+
+namespace bk
+{
+	int* no_alloc_status_word(int device) noexcept
+	{
+		if (device < 0 or device >= kMaxDevices)
+			return nullptr;
+		std::lock_guard<std::mutex> lock(address_mutex);
+		return reinterpret_cast<int*>(address[device]);
+	}
+} /* namespace bk */
 
 namespace avocado
 {
@@ -124,11 +145,19 @@ namespace avocado
 				if (tiles == 0 or channels == 0 or filters == 0)
 					return AVOCADO_STATUS_SUCCESS;
 				constexpr int planes = 16;
+				bk::ConvArgs args = { };
+				args.batch = batch, args.height = height, args.width = width, args.channels = channels, args.filters = filters;
+				args.out_height = height, args.out_width = width;
+				args.y = yPtr, args.bias = bPtr, args.z = zPtr, args.activation = activation;
+				/* the single-kernel contraction + output transform keeps M in TMEM; only the two-kernel form needs room for it */
+				const bool single_kernel = bk::winograd_f23_contract_output_covers(ctx, args, y.dtype, tiles);
+				if (not single_kernel and (channels % 8 != 0 or filters % 8 != 0))
+					return AVOCADO_STATUS_NOT_SUPPORTED;
 				const size_t u_bytes = align_up(static_cast<size_t>(planes) * filters * channels * 2, 256);
 				const size_t v_bytes = align_up(static_cast<size_t>(planes) * tiles * channels * 2, 256);
-				const size_t m_bytes = align_up(static_cast<size_t>(planes) * tiles * filters * 2, 256);
+				const size_t m_bytes = single_kernel ? 0 : align_up(static_cast<size_t>(planes) * tiles * filters * 2, 256);
 				/* the fixed array is all there is: a problem that does not fit is refused, never trimmed */
-				if (tiles > 0x7FFFFFFFll or u_bytes + v_bytes + m_bytes > kScratchBytes)
+				if (tiles > 0x7FFFFF00ll or u_bytes + v_bytes + m_bytes > kScratchBytes)
 					return AVOCADO_STATUS_BAD_PARAM;
 
 				unsigned char *base = nullptr;
@@ -140,8 +169,6 @@ namespace avocado
 				void *u_ptr = base + kStatusBytes;
 				void *v_ptr = base + kStatusBytes + u_bytes;
 				void *m_ptr = base + kStatusBytes + u_bytes + v_bytes;
-				if (cudaMemsetAsync(status_word, 0, kStatusBytes, ctx.getStream()) != cudaSuccess)
-					return checkForErrors();
 
 				const avDataType_t domain = AVOCADO_DTYPE_FLOAT16;
 				const TensorObject u = make_tensor(domain, { planes, filters, channels });
@@ -154,16 +181,9 @@ namespace avocado
 				status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr, status_word);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;
-				{
+				if (single_kernel)
 					/* the same single-kernel contraction + output transform the allocating entry point uses */
-					bk::ConvArgs args = { };
-					args.batch = batch, args.height = height, args.width = width, args.channels = channels, args.filters = filters;
-					args.out_height = height, args.out_width = width;
-					args.y = yPtr, args.bias = bPtr, args.z = zPtr, args.activation = activation;
-					status = bk::winograd_f23_contract_output(ctx, args, y.dtype, tiles, v_ptr, u_ptr, alpha1, alpha2, beta, status_word);
-					if (status != AVOCADO_STATUS_NOT_SUPPORTED)
-						return status;
-				}
+					return bk::winograd_f23_contract_output(ctx, args, y.dtype, tiles, v_ptr, u_ptr, alpha1, alpha2, beta, status_word);
 				status = bk::gemm_batched_nt_tensor_core(ctx, v, v_ptr, u, u_ptr, m, m_ptr, status_word);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;

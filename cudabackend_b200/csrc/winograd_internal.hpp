@@ -33,6 +33,10 @@ namespace bk
 	avocado::backend::avStatus_t gemm_batched_nt_tensor_core(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::TensorObject &a,
 			const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const avocado::backend::b200::TensorObject &c, void *cPtr,
 			int *deviceStatus);
+
+	/* Device address of the error word inside the fixed scratch array of cudaConvolutionWinogradFusedForwardNoAlloc on
+	 * this device, or null while no call of that entry point has resolved the array's address there yet. */
+	int* no_alloc_status_word(int device) noexcept;
 } /* namespace bk */
 
 #endif /* B200_WINOGRAD_INTERNAL_HPP_ */

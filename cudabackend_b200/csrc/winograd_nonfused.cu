@@ -486,12 +486,11 @@ namespace
 		constexpr int ring_bytes = 96 * 1024; /* shared memory per block for the halo ring: two blocks per SM stay resident */
 		g.stages = std::max(2, std::min(f43::kMaxStages, ring_bytes / g.stage_bytes));
 		const int smem_bytes = g.stages * g.stage_bytes + 128;
-		static bool configured[kMaxDevices] = { };
-		if (not configured[ctx.device])
+		static PerDeviceOnce configured;
+		if (configured.run(ctx.device, [&]() -> cudaError_t { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024 + 128); }) != cudaSuccess)
 		{
-			if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024 + 128) != cudaSuccess)
-				return checkForErrors();
-			configured[ctx.device] = true;
+			cudaGetLastError();
+			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);

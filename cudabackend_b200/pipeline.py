@@ -132,17 +132,23 @@ class WinogradNonFused:
         self.gemm(self.g, self.u, self.v, False, False)  # [planes, tiles, K] x [planes, K, C] -> [planes, tiles, C]
         self.output_transform(self.v, self.dx, use_bias=False, use_z=False)
 
-    def backward_weights(self):
-        """dw from x and dy: input transform of x, gradient transform of dy, (T, N) contraction over the tiles, update transform."""
-        self.input_transform()
+    def backward_weights(self, reuse_v=False):
+        """dw from x and dy: input transform of x, gradient transform of dy, (T, N) contraction over the tiles, update transform.
+
+        reuse_v=True skips the input transform: V still holds the transform of x that forward() wrote (nothing in between
+        may have overwritten it -- backward_data() does)."""
+        if not reuse_v:
+            self.input_transform()
         self.gradient_transform()
         self.gemm(self.g, self.v, self.mw, True, False)  # [planes, tiles, K]^T x [planes, tiles, C] -> [planes, K, C]
         self.update_transform()
 
     def training_step(self):
+        """forward, dW, dX.  dW runs right after the forward pass so that it can take V = input transform(x) from it
+        instead of recomputing it; dX comes last because its contraction writes its result into the V workspace."""
         self.forward()
+        self.backward_weights(reuse_v=True)
         self.backward_data()
-        self.backward_weights()
 
 
 class DirectConvolution:

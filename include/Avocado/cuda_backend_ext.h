@@ -46,6 +46,12 @@ DLL_PUBLIC avStatus_t cudaGetLastDeviceStatus(avContextDescriptor_t context, int
  * No counterpart in the reference. */
 DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, int limitMicroseconds);
 
+/* The same self test with the kernel pointed at the error word of cudaConvolutionWinogradFusedForwardNoAlloc's fixed
+ * array on the context's device (shared by all contexts of that device) instead of the context's own word: the report
+ * must surface through cudaGetLastDeviceStatus all the same.  Returns AVOCADO_STATUS_BAD_PARAM while no call of that
+ * entry point has been made on the device.  No counterpart in the reference. */
+DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTestNoAlloc(avContextDescriptor_t context, int limitMicroseconds);
+
 /* Orders two contexts on the device without blocking the host: everything enqueued on `waiting` after this call runs
  * after everything enqueued on `signalling` before it.  The reference has only cudaSynchronizeWithContext, which blocks
  * the calling thread; with this a caller can run independent steps on two contexts (for instance the weight transform
@@ -64,8 +70,8 @@ DLL_PUBLIC avStatus_t cudaContextEndCapture(avContextDescriptor_t context, av_in
 DLL_PUBLIC avStatus_t cudaContextLaunchGraph(avContextDescriptor_t context, av_int64 graph);
 DLL_PUBLIC avStatus_t cudaDestroyCapturedGraph(av_int64 graph);
 
-/* Size of the fixed scratch array behind cudaConvolutionWinogradFusedForwardNoAlloc.  Every GPU that loads the
- * library reserves this much device memory (plus 256 bytes) from load until the process exits. */
+/* Size of the fixed scratch array behind cudaConvolutionWinogradFusedForwardNoAlloc.  Every GPU on which the library's
+ * device code is loaded holds this much device memory (plus 256 bytes) until the process exits. */
 #define AVOCADO_NO_ALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
 
 /* cudaConvolutionWinogradFusedForward for callers that may not cause a device allocation -- a host that has given
@@ -76,11 +82,15 @@ DLL_PUBLIC avStatus_t cudaDestroyCapturedGraph(av_int64 graph);
  * workspace and allocates none because it was never finished).
  *  - float16 / bfloat16 tensors, 3x3 kernel, unit stride and dilation, C and K multiples of 8, y the size of x;
  *    anything else returns UNSUPPORTED_DATATYPE / NOT_SUPPORTED.
- *  - 32 * (K*C + tiles*C + tiles*K) bytes, tiles = N*ceil(H/2)*ceil(W/2), must fit AVOCADO_NO_ALLOC_SCRATCH_BYTES;
+ *  - 32 * (K*C + tiles*C) bytes, tiles = N*ceil(H/2)*ceil(W/2), must fit AVOCADO_NO_ALLOC_SCRATCH_BYTES (plus
+ *    32 * tiles*K when y, z or the bias is not 16 / 16 / 4-byte aligned, because the products are then written out);
  *    a larger problem returns AVOCADO_STATUS_BAD_PARAM and launches nothing.
- *  - The first call on a device resolves the array's device address; make it before any stream capture.
+ *  - The first call on a device resolves the array's device address and, with the runtime's lazy loading, is when the
+ *    driver places the array and the kernels on the device: make it at start-up, before the host's own pool takes the
+ *    remaining memory and before any stream capture.
  *  - All calls on one device share the array: calls that overlap on the GPU race.  It keeps the last call's contents;
- *    the only part that must start at zero, the kernel's 256-byte error word, is cleared by every call. */
+ *    the only part that must start at zero, the kernels' 256-byte error word, starts as zero and is cleared when
+ *    cudaGetLastDeviceStatus (of any context on the device) reads it, so a report is never lost. */
 DLL_PUBLIC avStatus_t cudaConvolutionWinogradFusedForwardNoAlloc(avContextDescriptor_t context, const avConvolutionDescriptor_t config, const void *alpha1,
 		const avTensorDescriptor_t xDesc, const avMemoryDescriptor_t xMem, const avTensorDescriptor_t wDesc, const avMemoryDescriptor_t wMem,
 		const avTensorDescriptor_t bDesc, const avMemoryDescriptor_t bMem, const void *alpha2, const avTensorDescriptor_t zDesc,

@@ -1,7 +1,7 @@
 """Builds oracle/_ref/libref_winograd.so from the REFERENCE's own sources.  TEST INFRASTRUCTURE ONLY.
 
-The reference's non-fused Winograd kernels (src/winograd_nonfused.cu) and its cuBLAS GEMM wrapper (src/gemm.cpp) are
-compiled unmodified, where they lie under the reference tree, against the stand-in header in oracle/ref_shim/ and the
+The reference's non-fused Winograd kernels (src/winograd_nonfused.cu), its cuBLAS GEMM wrapper (src/gemm.cpp) and its
+im2row lowering (src/im2row.cu) are compiled unmodified, where they lie under the reference tree, against the stand-in header in oracle/ref_shim/ and the
 type header of this repository, and linked with oracle/ref_harness.cu.  The reference targets sm_61 and does not
 compile natively for sm >= 80 (its bfloat16 number class is empty there), so the device code is emitted as compute_75
 PTX, which the driver JIT-compiles on the B200.  The output is a comparator for the GPU parity tests; nothing of the
@@ -13,6 +13,7 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
+# AVOCADO_REFERENCE_ROOT names the checkout of the reference; the default is where this project's build container mounts it
 REFERENCE_ROOT = os.environ.get("AVOCADO_REFERENCE_ROOT", "/root/reference")
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB = os.path.join(OUT_DIR, "libref_winograd.so")
@@ -20,10 +21,11 @@ LIB = os.path.join(OUT_DIR, "libref_winograd.so")
 
 def build(force=False):
     sources = [os.path.join(REFERENCE_ROOT, "src", "winograd_nonfused.cu"), os.path.join(REFERENCE_ROOT, "src", "gemm.cpp"),
-               os.path.join(HERE, "ref_harness.cu")]
+               os.path.join(REFERENCE_ROOT, "src", "im2row.cu"), os.path.join(HERE, "ref_harness.cu")]
     if not all(os.path.exists(s) for s in sources):
         raise RuntimeError("reference sources not found under %s" % REFERENCE_ROOT)
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= max(os.path.getmtime(s) for s in sources):
+    shim = os.path.join(HERE, "ref_shim", "Avocado", "backend_descriptors.hpp")
+    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= max(os.path.getmtime(s) for s in sources + [shim]):
         return LIB
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     os.makedirs(OUT_DIR, exist_ok=True)

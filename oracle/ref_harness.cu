@@ -1,11 +1,15 @@
 /*
  * ref_harness.cu -- drives the reference's own non-fused Winograd kernels.  TEST INFRASTRUCTURE ONLY.
  *
- * Linked with the reference's src/winograd_nonfused.cu and src/gemm.cpp (compiled unmodified, see build_ref.py).  It
- * supplies the two helpers those files take from translation units that are not compiled here (is_conv,
- * src/im2row.cu:75-81; cuda_sm_version, src/cuda_properties.cpp:121-140) and one C entry point that runs the chain of
- * ref app/CudaBackend.cu:401-420 (weight transform, input transform, batched GEMM, output transform) plus the dW
- * chain (gradient transform, GEMM(T,N), update transform) on host buffers and returns every intermediate.
+ * Linked with the reference's src/winograd_nonfused.cu, src/gemm.cpp and src/im2row.cu (compiled unmodified, see
+ * build_ref.py).  It supplies the helper those files take from a translation unit that is not compiled here
+ * (cuda_sm_version, src/cuda_properties.cpp:121-140) and two C entry points:
+ *   ref_winograd_chain     the chain of ref app/CudaBackend.cu:401-420 (weight transform, input transform, batched GEMM,
+ *                          output transform) plus the dW chain (gradient transform, GEMM(T,N), update transform) on host
+ *                          buffers, returning every intermediate;
+ *   ref_im2row_gemm_int8   the explicit lowering the reference's scratch test used for its int8 convolution
+ *                          (ref app/CudaBackend.cu:233-240): cudaIm2Row (src/im2row.cu:83-121) followed by the
+ *                          int8 -> int32 cudaGemm (src/gemm.cpp:42-57), i.e. the reference's own int32 accumulators.
  */
 #include <Avocado/cuda_backend.h>
 #include <Avocado/backend_descriptors.hpp>
@@ -20,13 +24,6 @@ namespace avocado
 	namespace backend
 	{
 		using namespace cuda;
-		bool is_conv(int expectedSize, const TensorDescriptor &wDesc) noexcept
-		{
-			for (int i = 0; i < wDesc.nbDims() - 2; i++)
-				if (wDesc.dimension(1 + i) != expectedSize)
-					return false;
-			return true;
-		}
 		int cuda_sm_version(int device) noexcept
 		{
 			int major = 0, minor = 0;
@@ -154,6 +151,46 @@ extern "C" int ref_winograd_chain(int dtype, int transformSize, int kernelSize, 
 			tg.download(g);
 			tmw.download(mw);
 			tdw.download(dw);
+		}
+	}
+	cublasDestroy(context.handle);
+	cudaStreamDestroy(context.stream);
+	return result;
+}
+
+/* x: int8 [N,H,W,C], w: int8 [K,3,3,C] (host).  rows (optional): int8 [N*H*W, 9*C]; acc: int32 [N*H*W, K].
+ * Returns 0 on success, otherwise 100*stage + avStatus_t of the failing call, or -1 for a CUDA error. */
+extern "C" int ref_im2row_gemm_int8(int N, int H, int W, int C, int K, const void *x, const void *w, void *rows, void *acc)
+{
+	cudaSetDevice(0);
+	ContextDescriptor context;
+	cudaStreamCreate(&context.stream);
+	cublasCreate(&context.handle);
+	cublasSetStream(context.handle, context.stream);
+	ConvolutionDescriptor conv;
+	conv.padding[0] = -1;
+	conv.padding[1] = -1;
+	const avContextDescriptor_t ctx = static_cast<avContextDescriptor_t>(reinterpret_cast<intptr_t>(&context));
+	const avConvolutionDescriptor_t cfg = static_cast<avConvolutionDescriptor_t>(reinterpret_cast<intptr_t>(&conv));
+	int result = 0;
+	{
+		Tensor tx(AVOCADO_DTYPE_INT8, { N, H, W, C }, 1), tw(AVOCADO_DTYPE_INT8, { K, 3, 3, C }, 1);
+		Tensor trows(AVOCADO_DTYPE_INT8, { N * H * W, 9 * C }, 1), tw2d(AVOCADO_DTYPE_INT8, { K, 9 * C }, 1), tacc(AVOCADO_DTYPE_INT32, { N * H * W, K }, 4);
+		tx.upload(x);
+		tw.upload(w);
+		tw2d.upload(w);
+		avStatus_t s = cudaIm2Row(ctx, cfg, tw.d(), tx.d(), tx.m(), trows.d(), trows.m());
+		if (s != AVOCADO_STATUS_SUCCESS)
+			result = 100 + s;
+		if (result == 0 and (s = cudaGemm(ctx, AVOCADO_GEMM_OPERATION_N, AVOCADO_GEMM_OPERATION_T, nullptr, trows.d(), trows.m(), tw2d.d(), tw2d.m(), nullptr,
+				tacc.d(), tacc.m())) != AVOCADO_STATUS_SUCCESS)
+			result = 200 + s;
+		if (cudaStreamSynchronize(context.stream) != cudaSuccess or cudaGetLastError() != cudaSuccess)
+			result = (result == 0) ? -1 : result;
+		if (result == 0)
+		{
+			trows.download(rows);
+			tacc.download(acc);
 		}
 	}
 	cublasDestroy(context.handle);

@@ -1,7 +1,7 @@
 /*
  * Stand-in for the reference's missing support header Avocado/backend_descriptors.hpp.  TEST INFRASTRUCTURE ONLY.
  *
- * The reference's hot-path sources (src/winograd_nonfused.cu, src/gemm.cpp, src/activations.cuh) include this header
+ * The reference's hot-path sources (src/winograd_nonfused.cu, src/gemm.cpp, src/im2row.cu, src/activations.cuh) include this header
  * from a support library that is not part of the reference tree.  This file supplies just the classes and lookup
  * functions those sources use, so that they can be compiled UNMODIFIED, where they lie, into oracle/_ref/ and run on
  * a GPU as the comparator for the parity tests.  Handles are pointers to the objects below, cast to the integer
@@ -114,7 +114,43 @@ namespace avocado
 						std::memcpy(&v, padding_value, sizeof(T));
 						return v;
 					}
+					/* unit stride and dilation, one group: the only case the comparator drives (src/im2row.cu:89) */
+					TensorDescriptor getOutputShape(const TensorDescriptor &x, const TensorDescriptor &w) const
+					{
+						TensorDescriptor y;
+						y.type = x.type;
+						y.rank = x.rank;
+						y.dims[0] = x.dims[0];
+						for (int i = 1; i < x.rank - 1; i++)
+							y.dims[i] = x.dims[i] - 2 * padding[i - 1] - (w.dims[i] - 1);
+						y.dims[x.rank - 1] = w.dims[0];
+						return y;
+					}
 			};
+			inline int dataTypeSize(avDataType_t dtype)
+			{
+				switch (dtype)
+				{
+					case AVOCADO_DTYPE_UINT8:
+					case AVOCADO_DTYPE_INT8:
+						return 1;
+					case AVOCADO_DTYPE_INT16:
+					case AVOCADO_DTYPE_FLOAT16:
+					case AVOCADO_DTYPE_BFLOAT16:
+						return 2;
+					case AVOCADO_DTYPE_INT32:
+					case AVOCADO_DTYPE_FLOAT32:
+						return 4;
+					case AVOCADO_DTYPE_INT64:
+					case AVOCADO_DTYPE_FLOAT64:
+					case AVOCADO_DTYPE_COMPLEX32:
+						return 8;
+					case AVOCADO_DTYPE_COMPLEX64:
+						return 16;
+					default:
+						return 0;
+				}
+			}
 
 			inline ContextDescriptor& getContext(avContextDescriptor_t h)
 			{

@@ -1,10 +1,13 @@
-"""Runs the reference's own Winograd kernels (oracle/_ref/libref_winograd.so) on seeded inputs.  TEST INFRASTRUCTURE ONLY.
+"""Runs the reference's own kernels (oracle/_ref/libref_winograd.so) on seeded inputs.  TEST INFRASTRUCTURE ONLY.
 
     python -m oracle.run_ref --out results.npz [--case NAME ...]
+    python -m oracle.run_ref --int8-fixture tests/golden/reference_int8.npz      (writes the committed int8 fixture)
 
 Runs in a process of its own: the comparator exports the same C symbol names as the product library, so the two are
 never loaded together.  For every case the .npz holds the inputs (already rounded to the storage type) and every
-tensor the reference produced: U, V, M, y and, for float32, the dW chain (G, Mw, dw).
+tensor the reference produced: U, V, M, y and, for float32, the dW chain (G, Mw, dw).  The int8 cases hold the int32
+accumulators of the reference's explicit lowering (cudaIm2Row + int8 cudaGemm): its quantised convolution without the
+requantisation it never had.
 """
 import argparse
 import ctypes
@@ -28,6 +31,36 @@ CASES = {
     "refshape_f43_fp32": ("float32", 4, 3, 12, 13, 14, 135, 21, 27),
 }
 SMALL = [name for name in CASES if name.startswith("small_")]
+
+# int8 cases: name -> (N, H, W, C, K, seed); "golden" takes x and w from tests/golden/int8_requant.npz instead
+INT8_CASES = {
+    "int8_golden": None,
+    "int8_14x14_c64": (4, 14, 14, 64, 64, 31),
+    "int8_ragged": (3, 9, 7, 32, 48, 32),
+}
+GOLDEN_INT8 = os.path.join(os.path.dirname(HERE), "tests", "golden", "int8_requant.npz")
+
+
+def make_int8_inputs(name):
+    if INT8_CASES[name] is None:
+        golden = np.load(GOLDEN_INT8)
+        return golden["x"], golden["w"]
+    n, h, w, c, k, seed = INT8_CASES[name]
+    r = np.random.default_rng(seed)
+    return r.integers(-127, 128, (n, h, w, c), dtype=np.int8), r.integers(-127, 128, (k, 3, 3, c), dtype=np.int8)
+
+
+def run_int8_case(lib, name):
+    x, wt = make_int8_inputs(name)
+    n, h, w, c = x.shape
+    k = wt.shape[0]
+    rows = np.zeros((n * h * w, 9 * c), np.int8)
+    acc = np.zeros((n, h, w, k), np.int32)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    status = lib.ref_im2row_gemm_int8(n, h, w, c, k, p(np.ascontiguousarray(x)), p(np.ascontiguousarray(wt)), p(rows), p(acc))
+    if status != 0:
+        raise RuntimeError("reference im2row + int8 gemm failed for %s with code %d" % (name, status))
+    return {"x": x, "w": wt, "rows": rows, "acc": acc}
 
 
 def make_inputs(name):
@@ -63,18 +96,29 @@ def run_case(lib, name):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--out", required=True)
+    parser.add_argument("--out", default=None)
     parser.add_argument("--case", action="append", default=None)
+    parser.add_argument("--int8-fixture", default=None, help="write the reference's int32 accumulators of the golden int8 case to this file")
     args = parser.parse_args()
+    if args.out is None and args.int8_fixture is None:
+        parser.error("give --out and/or --int8-fixture")
     if not os.path.exists(LIB):
         print("comparator library not built: run python oracle/build_ref.py where the reference sources are mounted", file=sys.stderr)
         return 2
     lib = ctypes.CDLL(LIB)
     lib.ref_winograd_chain.restype = ctypes.c_int
     lib.ref_winograd_chain.argtypes = [ctypes.c_int] * 8 + [ctypes.c_void_p] * 11 + [ctypes.c_int]
+    lib.ref_im2row_gemm_int8.restype = ctypes.c_int
+    lib.ref_im2row_gemm_int8.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 4
+    if args.int8_fixture is not None:
+        result = run_int8_case(lib, "int8_golden")
+        np.savez_compressed(args.int8_fixture, acc=result["acc"], rows=result["rows"])
+    if args.out is None:
+        return 0
     flat = {}
-    for name in (args.case or list(CASES)):
-        for key, value in run_case(lib, name).items():
+    for name in (args.case or (list(CASES) + list(INT8_CASES))):
+        runner = run_int8_case if name in INT8_CASES else run_case
+        for key, value in runner(lib, name).items():
             flat[name + "/" + key] = value
     np.savez_compressed(args.out, **flat)
     return 0

@@ -160,3 +160,18 @@ def test_oracle_matches_reference_kernel_outputs():
             assert rel(g("mw"), mw) <= 8 * eps, name
             dw = o.conv2d_backward_weights(g("x"), g("dy"), (ks, ks), (pad, pad))
             assert o.error_metrics(g("dw"), dw)["elem"] <= 1e-4, name
+
+
+def test_oracle_int8_accumulators_match_the_reference():
+    """tests/golden/reference_int8.npz holds what the REFERENCE's own quantised path produced on a B200 for the inputs of
+    tests/golden/int8_requant.npz: its cudaIm2Row (src/im2row.cu:83-121) followed by its int8 -> int32 cudaGemm
+    (src/gemm.cpp:42-57), both compiled unmodified into oracle/_ref and driven by oracle/run_ref.py --int8-fixture.
+    The reference has no requantisation, so its int32 accumulators are as far as it can pin the int8 path: the
+    oracle's exact integer convolution, its im2row and the accumulators stored in the golden file must equal them
+    bit for bit."""
+    golden = np.load(os.path.join(GOLDEN, "int8_requant.npz"))
+    reference = np.load(os.path.join(GOLDEN, "reference_int8.npz"))
+    n, h, w, c = golden["x"].shape
+    assert np.array_equal(o.conv2d_forward_int8(golden["x"], golden["w"], None, int32_output=True), reference["acc"])
+    assert np.array_equal(golden["acc"] - golden["bias"][None, None, None, :], reference["acc"])
+    assert np.array_equal(o.im2row(golden["x"], (3, 3), (-1, -1)).reshape(n * h * w, 9 * c), reference["rows"])

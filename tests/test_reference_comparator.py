@@ -1,10 +1,12 @@
 """GPU tests against the reference's own kernels, run live.
 
-oracle/_ref/libref_winograd.so is the reference's src/winograd_nonfused.cu and src/gemm.cpp compiled unmodified (as
+oracle/_ref/libref_winograd.so is the reference's src/winograd_nonfused.cu, src/gemm.cpp and src/im2row.cu compiled unmodified (as
 compute_75 PTX, JIT-compiled on the B200) with oracle/build_ref.py.  It is run in a process of its own by
 oracle/run_ref.py.  Two claims are checked on the same seeded inputs:
   1. the CPU oracle reproduces the reference's transforms (this pins the oracle);
-  2. this library's result is no further from the exact float64 convolution than the reference's.
+  2. this library's result is no further from the exact float64 convolution than the reference's;
+  3. the int32 accumulators of the reference's own quantised path (cudaIm2Row + int8 cudaGemm) equal the oracle's and
+     this library's bit for bit (the reference has no requantisation, so this is as far as it can pin the int8 path).
 The library is built where the reference sources are mounted; on a machine without it the test reports a skip.
 """
 import os
@@ -14,7 +16,7 @@ import sys
 import numpy as np
 import pytest
 
-from cudabackend_b200 import pipeline
+from cudabackend_b200 import api, pipeline
 from oracle import oracle as o
 from oracle import run_ref
 
@@ -64,3 +66,22 @@ def test_library_is_no_worse_than_the_reference(ctx, reference_outputs, name):
         p.backward_weights()
         exact_dw = o.conv2d_backward_weights(g("x"), g("dy"), (ks, ks), (pad, pad))
         assert o.error_metrics(p.dw.download(ctx), exact_dw)["elem"] <= max(1.05 * o.error_metrics(g("dw"), exact_dw)["elem"], 2e-5)
+
+
+@pytest.mark.parametrize("name", list(run_ref.INT8_CASES))
+def test_int8_accumulators_equal_the_reference(ctx, reference_outputs, name):
+    x = reference_outputs[name + "/x"]
+    wt = reference_outputs[name + "/w"]
+    reference_acc = reference_outputs[name + "/acc"]
+    n, h, w, c = x.shape
+    k = wt.shape[0]
+    # the oracle's exact integer convolution (no bias, int32 out) against the reference's lowering + cuBLAS product
+    assert np.array_equal(o.conv2d_forward_int8(x, wt, None, int32_output=True), reference_acc)
+    # the oracle's im2row against the reference's row matrix
+    assert np.array_equal(o.im2row(x, (3, 3), (-1, -1)).reshape(n * h * w, 9 * c), reference_outputs[name + "/rows"])
+    # this library, int32 output: the raw accumulators of the implicit-GEMM entry point
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "int8", out_dtype="int32")
+    d.x.upload(ctx, x)
+    d.wt.upload(ctx, wt)
+    d.implicit_gemm()
+    assert np.array_equal(d.y.download_raw(ctx), reference_acc)

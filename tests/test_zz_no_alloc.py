@@ -45,16 +45,64 @@ def test_no_alloc_matches_allocating_entry_point_twice_in_a_row(ctx, dtype):
 
         # same kernels in the same order: the two entry points agree bit for bit ...
         assert np.array_equal(got, expected)
+        # ... and no bounded wait ran out on either path (the fixed array's own error word is read here too)
+        assert ctx.last_device_status() == 0
         # ... and both are within the stated tolerance of the float64 oracle
         y0_stored = api.to_storage(y0, dtype)[1]
         ref = o.conv2d_forward(x, wt, bias=b, z=z, y=y0_stored, alpha1=f(1.1), alpha2=f(1.2), beta=f(0.1), activation="relu")
         assert o.error_metrics(api.from_storage(got, dtype), ref)["elem"] <= common.TOLERANCE[dtype]
 
 
+def test_no_alloc_second_call_takes_no_device_memory(ctx):
+    """The claim in the name: once the first call on the device has been made, further calls leave the amount of free
+    device memory exactly where it was (the array and the kernels were placed by that first call)."""
+    torch = pytest.importorskip("torch")
+    d, _, _, _, _ = build(ctx, 2, 16, 16, 64, 64, "float16", 5)
+    d.winograd_fused_no_alloc(activation="relu")
+    ctx.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    for _ in range(3):
+        d.winograd_fused_no_alloc(activation="relu")
+    ctx.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before
+
+
+def test_no_alloc_two_kernel_form_when_y_is_misaligned(ctx):
+    """y eight bytes off a 16-byte boundary: the single-kernel contraction + output transform does not apply, both entry
+    points write the products out and run the output transform as a kernel of its own -- still bit-identical."""
+    d, x, wt, b, z = build(ctx, 2, 12, 12, 32, 32, "float16", 7)
+    backing = api.Memory(d.y.desc.nbytes + 16, 0)
+    aligned_mem, d.y.mem = d.y.mem, backing.view(d.y.desc.nbytes, 8)
+    d.winograd_fused(alpha2=0.5, activation="relu")
+    expected = d.y.download_raw(ctx)
+    d.y.mem.zero(ctx)
+    d.winograd_fused_no_alloc(alpha2=0.5, activation="relu")
+    got = d.y.download_raw(ctx)
+    assert np.array_equal(got, expected)
+    ref = o.conv2d_forward(x, wt, bias=b, z=z, alpha2=0.5, activation="relu")
+    assert o.error_metrics(api.from_storage(got, "float16"), ref)["elem"] <= common.TOLERANCE["float16"]
+    assert ctx.last_device_status() == 0
+    d.y.mem = aligned_mem
+
+
+def test_no_alloc_error_word_reaches_the_caller(ctx):
+    """A bounded wait that runs out on this path is recorded in a word inside the fixed array; cudaGetLastDeviceStatus
+    must report it (and clear it) like the context's own word.  The self test makes such a wait run out harmlessly."""
+    d, _, _, _, _ = build(ctx, 1, 8, 8, 32, 32, "float16", 9)
+    d.winograd_fused_no_alloc()  # resolves the array's address on this device
+    assert ctx.last_device_status() == 0
+    api.call("cudaRunBoundedWaitSelfTestNoAlloc", ctx.handle, 200)
+    assert ctx.last_device_status() == 1 << 5
+    assert ctx.last_device_status() == 0
+    d.winograd_fused_no_alloc()  # the path still works afterwards
+    assert ctx.last_device_status() == 0
+
+
 def test_no_alloc_rejects_what_does_not_fit(ctx):
-    # 16 * 2 * (K*C + tiles*C + tiles*K) with tiles = 8*28*28 is about 25.8 MB, beyond the 8 MiB array
+    # 16 * 2 * (K*C + tiles*C) with tiles = 8*28*28 is about 13 MB, beyond the 8 MiB array
     d, _, _, _, _ = build(ctx, 8, 56, 56, 64, 64, "float16", 0)
-    need = 32 * (64 * 64 + 2 * 8 * 28 * 28 * 64)
+    need = 32 * (64 * 64 + 8 * 28 * 28 * 64)
     assert need > api.NO_ALLOC_SCRATCH_BYTES
     with pytest.raises(api.AvocadoError) as failure:
         d.winograd_fused_no_alloc()
