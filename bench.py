@@ -238,6 +238,9 @@ class Workload:
         self.cfg = cfg
         self.ctx = api.Context(device)
         self.fusion = fusion
+        if fusion:
+            # opt-in of the library: cudaGemmBatched + cudaWinogradOutputTransform of the pipeline run as one kernel
+            self.ctx.set_winograd_fusion(True)
         n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
         kind = cfg["kind"]
         stored = {}
@@ -280,6 +283,9 @@ class Workload:
         """(name, callable) pairs making up one step, in issue order."""
         kind = self.cfg["kind"]
         p = self.p
+        if kind == "winograd_nonfused" and self.fusion:
+            return [("weight_transform", p.weight_transform), ("input_transform", p.input_transform),
+                    ("gemm_output_fused", lambda: (p.gemm(p.v, p.u, p.m, False, True), p.output_transform()))]
         if kind == "winograd_nonfused":
             return [("weight_transform", p.weight_transform), ("input_transform", p.input_transform),
                     ("gemm", lambda: p.gemm(p.v, p.u, p.m, False, True)), ("output_transform", p.output_transform)]
@@ -333,23 +339,27 @@ class Workload:
 
 
 def stage_bytes(cfg, matrices_dtype):
-    """Algorithmic bytes of each stage of the non-fused pipeline (inputs read once, outputs written once)."""
+    """Algorithmic bytes of each stage of the non-fused pipeline (inputs read once, outputs written once).
+    gemm_output_fused is the contraction + output transform as one kernel: V and U read, y written, M never in memory."""
     n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
     b = elem_size(cfg["dtype"])
     mb = elem_size(matrices_dtype)
     t = n * ((h + 3) // 4) * ((w + 3) // 4)
     return {"weight_transform": 9 * k * c * b + 36 * k * c * mb, "input_transform": n * h * w * c * b + 36 * t * c * mb,
             "gemm": 36 * t * c * mb + 36 * k * c * mb + 36 * t * k * mb, "output_transform": 36 * t * k * mb + n * h * w * k * b,
+            "gemm_output_fused": 36 * t * c * mb + 36 * k * c * mb + n * h * w * k * b,
             "gemm_flops": 2.0 * 36 * t * c * k}
 
 
-def algorithmic_bytes(cfg, matrices_dtype):
+def algorithmic_bytes(cfg, matrices_dtype, fusion=False):
     """Bytes one step must move when every tensor is read once and written once (the figures the rooflines use)."""
     n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
     b = elem_size(cfg["dtype"])
     kind = cfg["kind"]
     if kind == "winograd_nonfused":
         sb = stage_bytes(cfg, matrices_dtype)
+        if fusion:
+            return sb["weight_transform"] + sb["input_transform"] + sb["gemm_output_fused"]
         return sb["weight_transform"] + sb["input_transform"] + sb["gemm"] + sb["output_transform"]
     if kind == "winograd_fused":
         # a fully fused convolution: x and w in, y out, the float32 bias; no transform-domain tensor touches memory
@@ -438,7 +448,7 @@ class Measurement:
         self.matrices = matrices_dtype if cfg["kind"] in ("winograd_nonfused", "training") else None
         if cfg["kind"] == "training":
             self.matrices = "float32"
-        self.fusion = fusion and cfg["kind"] == "winograd_nonfused"
+        self.fusion = fusion and cfg["kind"] == "winograd_nonfused" and self.matrices in ("float16", "bfloat16")
         self.data = synthetic(cfg, seed_offset=seed_offset)
         self.rotation = args.rotation
         self.sets = [Workload(cfg, local_rank, self.matrices, self.data, fusion=self.fusion, keep_inputs=(i == 0)) for i in range(self.rotation)]
@@ -742,15 +752,23 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
     flops = direct_flops(cfg)
     if kind == "winograd_nonfused":
         sb = stage_bytes(cfg, matrices)
-        total = algorithmic_bytes(cfg, matrices)
-        gemm_s = stage_ms["gemm"] * 1e-3
-        achieved = sb["gemm"] / gemm_s / 1e9
-        name = "kernel_gemm_nt_tc" if matrices != "float32" else "kernel_gemm_nt_tf32x3"
-        rec = {"kernel": name + " (transform-domain batched GEMM)", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-               "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get((m.config_id, matrices, False)), "algorithmic_bytes": sb["gemm"],
+        total = algorithmic_bytes(cfg, matrices, m.fusion)
+        dominant = "gemm_output_fused" if m.fusion else "gemm"
+        gemm_s = stage_ms[dominant] * 1e-3
+        achieved = sb[dominant] / gemm_s / 1e9
+        if m.fusion:
+            name = "kernel_f43_contract_output (transform-domain contraction + output transform in one kernel; M stays in TMEM)"
+        else:
+            name = ("kernel_gemm_nt_tc" if matrices != "float32" else "kernel_gemm_nt_tf32x3") + " (transform-domain batched GEMM)"
+        rec = {"kernel": name, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+               "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get((m.config_id, matrices, m.fusion)), "algorithmic_bytes": sb[dominant],
                "device_copy_of_same_bytes": copy_reference, "peak_source": peaks["source"], "tensor_tflops": sb["gemm_flops"] / gemm_s / 1e12,
                "tensor_frac": sb["gemm_flops"] / gemm_s / 1e12 / peaks["bf16_tflops"],
                "pipeline": {"algorithmic_bytes": total, "achieved": total / step_s / 1e9, "frac": total / step_s / 1e9 / peaks["hbm_gbs"]}}
+        if m.fusion:
+            unfused = algorithmic_bytes(cfg, matrices, False)
+            rec["pipeline"]["unfused_algorithmic_bytes"] = unfused
+            rec["pipeline"]["frac_on_unfused_bytes"] = unfused / step_s / 1e9 / peaks["hbm_gbs"]
         names = [n for n in stage_ms if n in sb]
         rec["stage_gbs"] = {n: sb[n] / (stage_ms[n] * 1e-3) / 1e9 for n in names}
         rec["stage_hbm_frac"] = {n: rec["stage_gbs"][n] / peaks["hbm_gbs"] for n in names}
@@ -784,12 +802,12 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
 
 
 def sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_peaks, sampler, per_gpu_batch=None, steps_per_graph=1,
-               want_parity=True, want_sustained=True, want_stages=True):
+               want_parity=True, want_sustained=True, want_stages=True, fusion=False):
     """Device-timed record of one configuration: value, roofline, parity, sustained."""
     cfg = dict(CONFIGS[config_id])
     if per_gpu_batch is not None:
         cfg["n"] = per_gpu_batch
-    m = Measurement(args, config_id, cfg, matrices or cfg["dtype"], rank, world, local_rank, seed_offset=rank)
+    m = Measurement(args, config_id, cfg, matrices or cfg["dtype"], rank, world, local_rank, seed_offset=rank, fusion=fusion)
     m.capture(steps_per_graph)
     steps = max(args.steps, 20)
     ms, done, clocks, wall_ms = m.timed(steps, args.warmup, sampler if rank == 0 else None)
@@ -955,14 +973,14 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
 
     # ---- headline: the configured workload, every rank its own batch ---------------------------------------
     matrices_dtype = args.matrices or cfg["dtype"]
-    m = Measurement(args, args.config, cfg, matrices_dtype, rank, world, local_rank, seed_offset=rank)
+    m = Measurement(args, args.config, cfg, matrices_dtype, rank, world, local_rank, seed_offset=rank, fusion=not args.no_fusion)
     m.capture(1)
     elapsed_ms, done, clocks, wall_ms = m.timed(args.steps, args.warmup, sampler if rank == 0 else None)
     ms_per_step = elapsed_ms / done
     stage_ms = m.stage_times(max(20, min(args.steps, 200)))
     copy_reference = None
     if cfg["kind"] == "winograd_nonfused":
-        copy_reference = m.copy_reference(stage_bytes(cfg, m.matrices)["gemm"], max(20, min(args.steps, 200)))
+        copy_reference = m.copy_reference(stage_bytes(cfg, m.matrices)["gemm_output_fused" if m.fusion else "gemm"], max(20, min(args.steps, 200)))
     m.check_status()
     parity = None
     if rank == 0 and not args.no_parity:
@@ -991,6 +1009,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                                                "int8": "s8 (s32 accumulate)"}[cfg["dtype"]],
                 "data": "synthetic",
                 "config": {"workload": cfg["name"], "per_gpu_batch": cfg["n"], "global_batch": cfg["n"] * world, "matrices_dtype": m.matrices,
+                           "fusion": ("cudaContextSetWinogradFusion on: cudaGemmBatched + cudaWinogradOutputTransform run as one kernel, M is not written"
+                                      if m.fusion else "off: every call is its own kernel"),
                            "l2": "rotating %d buffer sets; each set's working set is re-read only after %d other steps" % (m.rotation, m.rotation - 1),
                            "parallelism": "batch sharded, dp%d: every rank runs the configuration's batch (weak scaling); the split of the "
                                           "configuration's own batch over the ranks is under `sharded`" % world},
@@ -1030,7 +1050,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             for key, config_id, matrices in (("cfg2", 2, None), ("cfg3", 3, None), ("cfg4", 4, None)):
                 first, last = sharding.shard_bounds(CONFIGS[config_id]["n"], world, rank)
                 record = sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_peaks, sampler, per_gpu_batch=last - first,
-                                    steps_per_graph=args.rotation, want_parity=False, want_sustained=False, want_stages=False)
+                                    steps_per_graph=args.rotation, want_parity=False, want_sustained=False, want_stages=False,
+                                    fusion=(config_id == 2 and not args.no_fusion))
                 if rank == 0:
                     record["scaling"] = "strong"
                     record["global_batch"] = CONFIGS[config_id]["n"]
@@ -1072,6 +1093,8 @@ def main():
     parser.add_argument("--only-headline", action="store_true", help="skip the sub-records of the other configurations")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     parser.add_argument("--no-parity", action="store_true", help="skip the comparison of the outputs with the CPU oracle")
+    parser.add_argument("--no-fusion", action="store_true",
+                        help="keep cudaGemmBatched and cudaWinogradOutputTransform as two kernels (the library's default without the opt-in)")
     parser.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a captured graph")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -84,6 +84,7 @@ SIGNATURES = {
     "cudaRunBoundedWaitSelfTest": (_INT, [_H, _INT]),
     "cudaRunBoundedWaitSelfTestNoAlloc": (_INT, [_H, _INT]),
     "cudaContextWaitForContext": (_INT, [_H, _H]),
+    "cudaContextSetWinogradFusion": (_INT, [_H, _INT]),
     "cudaIm2Row": (_INT, [_H, _H, _H, _H, _H, _H, _H]),
     "cudaOptimizerLearn": (_INT, [_H, _H, _VP, _H, _H, _VP, _H, _H, _H]),
     "cudaAddBias": (_INT, [_H, _VP, _VP, _H, _H, _H, _H, _H, _H, _VP, _VP, _VP, _H, _INT]),
@@ -182,6 +183,10 @@ class Context:
         r = _INT(0)
         call("cudaGetLastDeviceStatus", self.handle, ctypes.byref(r))
         return int(r.value)
+
+    def set_winograd_fusion(self, enabled):
+        """Lets cudaGemmBatched + cudaWinogradOutputTransform of an F(4x4,3x3) pipeline run as one kernel (the products M are then not written)."""
+        call("cudaContextSetWinogradFusion", self.handle, 1 if enabled else 0)
 
     def wait_for(self, other):
         """Work enqueued on this context from now on runs after the work already enqueued on `other` (no host blocking)."""

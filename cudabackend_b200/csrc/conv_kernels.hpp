@@ -30,6 +30,14 @@ namespace bk
 	avocado::backend::avStatus_t winograd_f23_contract_output(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args,
 			avocado::backend::avDataType_t yType, long long tiles, const void *vPtr, const void *uPtr, const void *alpha1, const void *alpha2, const void *beta,
 			int *deviceStatus);
+
+	/* Contraction + output transform of the non-fused F(4x4,3x3) pipeline in one kernel: reads V[36][tiles][C] and
+	 * U[36][K][C] (both float16 or both bfloat16), writes y[N][H][W][K] (float16 / bfloat16) with the bias / z / activation /
+	 * beta epilogue of cudaWinogradOutputTransform.  Returns NOT_SUPPORTED, launching nothing, outside what it covers. */
+	avocado::backend::avStatus_t winograd_f43_contract_output(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::TensorObject &v,
+			const void *vPtr, const avocado::backend::b200::TensorObject &u, const void *uPtr, const avocado::backend::b200::TensorObject &y, void *yPtr,
+			const void *biasPtr, const void *zPtr, const void *alpha1, const void *alpha2, const void *beta,
+			avocado::backend::avActivationType_t activation, int *deviceStatus);
 } /* namespace bk */
 
 #endif /* B200_CONV_KERNELS_HPP_ */

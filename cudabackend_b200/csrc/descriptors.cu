@@ -12,6 +12,7 @@
 #include "winograd_internal.hpp"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 
 namespace avocado
@@ -227,11 +228,27 @@ namespace avocado
 			{
 				return handle >= 0 and handle_kind(handle) == Kind::Context and handle_is_default(handle);
 			}
-			ContextObject& getContext(avContextDescriptor_t handle)
+			ContextObject& getContextKeepDeferred(avContextDescriptor_t handle)
 			{
 				if (isDefault(handle))
 					return default_context(static_cast<int>(handle_slot(handle)));
 				return contextPool().get(handle);
+			}
+			ContextObject& getContext(avContextDescriptor_t handle)
+			{
+				ContextObject &ctx = getContextKeepDeferred(handle);
+				if (ctx.deferred.valid and bk::flush_deferred_gemm(ctx) != AVOCADO_STATUS_SUCCESS)
+					throw std::runtime_error("the batched GEMM held back on this context failed to launch");
+				return ctx;
+			}
+			static std::atomic<int> deferred_contexts { 0 };
+			int deferredCount() noexcept
+			{
+				return deferred_contexts.load();
+			}
+			void noteDeferred(int delta) noexcept
+			{
+				deferred_contexts.fetch_add(delta);
 			}
 			MemoryObject& getMemory(avMemoryDescriptor_t handle)
 			{
@@ -401,6 +418,8 @@ namespace avocado
 			std::unique_ptr<ContextObject> object = contextPool().remove(desc);
 			if (object == nullptr)
 				return AVOCADO_STATUS_BAD_PARAM;
+			if (object->deferred.valid)
+				bk::flush_deferred_gemm(*object); /* the caller asked for that product: it is not dropped with the context */
 			object.reset();
 			return AVOCADO_STATUS_SUCCESS;
 		}
@@ -484,6 +503,14 @@ namespace avocado
 		}
 		avStatus_t cudaDestroyMemoryDescriptor(avMemoryDescriptor_t desc)
 		{
+			/* a batched GEMM that some context is holding back may read or write this memory: launch it before the memory
+			 * goes (freeing waits for launched work, as it does for every other kernel) */
+			if (deferredCount() > 0)
+				contextPool().for_each([](ContextObject &ctx)
+				{
+					if (ctx.deferred.valid)
+						bk::flush_deferred_gemm(ctx);
+				});
 			std::unique_ptr<MemoryObject> object = memoryPool().remove(desc);
 			if (object == nullptr)
 				return AVOCADO_STATUS_FREE_FAILED;
@@ -863,6 +890,17 @@ namespace avocado
 					combined |= value;
 				}
 				result[0] = combined;
+				return AVOCADO_STATUS_SUCCESS;
+			AVOCADO_API_END
+		}
+
+		avStatus_t cudaContextSetWinogradFusion(avContextDescriptor_t context, int enabled)
+		{
+			AVOCADO_API_BEGIN
+				if (isDefault(context))
+					return AVOCADO_STATUS_BAD_PARAM;
+				ContextObject &ctx = getContext(context); /* launches whatever was held back under the old setting */
+				ctx.fuse_winograd = (enabled != 0);
 				return AVOCADO_STATUS_SUCCESS;
 			AVOCADO_API_END
 		}

@@ -707,6 +707,66 @@ namespace bk
 		return gemm_dispatch(ctx, s, a.dtype, c.dtype, alpha, beta, aPtr, bPtr, cPtr);
 	}
 
+	avStatus_t flush_deferred_gemm(ContextObject &ctx)
+	{
+		if (not ctx.deferred.valid)
+			return AVOCADO_STATUS_SUCCESS;
+		const DeferredGemm d = ctx.deferred;
+		ctx.deferred.valid = false;
+		noteDeferred(-1);
+		return gemm_batched(ctx, false, true, nullptr, d.a, d.aPtr, d.b, d.bPtr, nullptr, d.c, d.cPtr);
+	}
+
+	/* Whether this cudaGemmBatched call is the contraction M = V x U^T of an F(4x4,3x3) pipeline in a form the fused
+	 * contraction + output transform kernel can take over: 36 planes, (N, T), 16-bit, alpha = 1, beta = 0, and within what
+	 * the tensor-core kernel covers (so that launching it later, unfused, behaves exactly like launching it now). */
+	static bool deferrable(const ContextObject &ctx, bool transA, bool transB, const void *alpha, const TensorObject &a, const void *aPtr,
+			const TensorObject &b, const void *bPtr, const void *beta, const TensorObject &c, const void *cPtr)
+	{
+		if (not ctx.fuse_winograd or ctx.is_default or transA or not transB)
+			return false;
+		if (a.nb_dims != 3 or b.nb_dims != 3 or c.nb_dims != 3 or a.dims[0] != 36 or b.dims[0] != 36 or c.dims[0] != 36)
+			return false;
+		if (a.dtype != b.dtype or a.dtype != c.dtype or (a.dtype != AVOCADO_DTYPE_FLOAT16 and a.dtype != AVOCADO_DTYPE_BFLOAT16))
+			return false;
+		if (getAlphaValue<float>(alpha) != 1.0f or getBetaValue<float>(beta) != 0.0f)
+			return false;
+		if (a.dims[2] != b.dims[2] or c.dims[1] != a.dims[1] or c.dims[2] != b.dims[1] or a.dims[1] < 1)
+			return false;
+		if (aPtr == nullptr or bPtr == nullptr or cPtr == nullptr)
+			return false;
+		GemmShape s;
+		s.batch = 36;
+		s.transA = false;
+		s.transB = true;
+		s.M = a.dims[1];
+		s.Kc = a.dims[2];
+		s.N = b.dims[1];
+		s.lda = s.Kc;
+		s.ldb = s.Kc;
+		s.ldc = s.N;
+		s.strideA = a.volumeWithoutFirstDim();
+		s.strideB = b.volumeWithoutFirstDim();
+		s.strideC = c.volumeWithoutFirstDim();
+		return tc_eligible(ctx, s, c.dtype, aPtr, bPtr, cPtr, 0.0f);
+	}
+
+	bool defer_gemm_batched(ContextObject &ctx, bool transA, bool transB, const void *alpha, const TensorObject &a, const void *aPtr, const TensorObject &b,
+			const void *bPtr, const void *beta, const TensorObject &c, void *cPtr)
+	{
+		if (not deferrable(ctx, transA, transB, alpha, a, aPtr, b, bPtr, beta, c, cPtr))
+			return false;
+		ctx.deferred.valid = true;
+		ctx.deferred.a = a;
+		ctx.deferred.b = b;
+		ctx.deferred.c = c;
+		ctx.deferred.aPtr = aPtr;
+		ctx.deferred.bPtr = bPtr;
+		ctx.deferred.cPtr = cPtr;
+		noteDeferred(+1);
+		return true;
+	}
+
 	avStatus_t gemm_batched_nt_tensor_core(ContextObject &ctx, const TensorObject &a, const void *aPtr, const TensorObject &b, const void *bPtr,
 			const TensorObject &c, void *cPtr, int *deviceStatus)
 	{
@@ -779,7 +839,13 @@ namespace avocado
 				const void *beta, const avTensorDescriptor_t cDesc, avMemoryDescriptor_t cMem)
 		{
 			AVOCADO_API_BEGIN
-				return bk::gemm_batched(getContext(context), is_transpose(aOp), is_transpose(bOp), alpha, getTensor(aDesc), getPointer(aMem), getTensor(bDesc),
+				ContextObject &ctx = getContext(context); /* a call held back earlier is launched first */
+				/* with fusion switched on, the contraction of an F(4x4,3x3) pipeline is held back until the next call shows
+				 * whether the output transform consumes it directly */
+				if (ctx.fuse_winograd and bk::defer_gemm_batched(ctx, is_transpose(aOp), is_transpose(bOp), alpha, getTensor(aDesc), getPointer(aMem),
+						getTensor(bDesc), getPointer(bMem), beta, getTensor(cDesc), getPointer(cMem)))
+					return AVOCADO_STATUS_SUCCESS;
+				return bk::gemm_batched(ctx, is_transpose(aOp), is_transpose(bOp), alpha, getTensor(aDesc), getPointer(aMem), getTensor(bDesc),
 						getPointer(bMem), beta, getTensor(cDesc), getPointer(cMem));
 			AVOCADO_API_END
 		}

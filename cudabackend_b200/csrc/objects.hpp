@@ -169,6 +169,19 @@ namespace avocado
 				bool flags[4] = { false, false, false, false };
 			};
 
+			/* A cudaGemmBatched call that a context with Winograd fusion switched on has accepted but not launched yet:
+			 * M = V x U^T of the F(4x4,3x3) pipeline, waiting to see whether the next call on the context is the output
+			 * transform of exactly that M (then one kernel does both and M is never written) or anything else (then the
+			 * batched GEMM is launched first, as if it had never been held back). */
+			struct DeferredGemm
+			{
+				bool valid = false;
+				TensorObject a, b, c;
+				const void *aPtr = nullptr;
+				const void *bPtr = nullptr;
+				void *cPtr = nullptr;
+			};
+
 			/* One stream on one device, a grow-only scratch buffer and a device-resident error word that kernels
 			 * with bounded waits set when a wait runs out. */
 			struct ContextObject
@@ -181,6 +194,8 @@ namespace avocado
 				int *device_status = nullptr;
 				cudaEvent_t order_event = nullptr; /* recorded on this stream when another context waits for this one */
 				std::mutex lazy_mutex; /* guards the first allocation of workspace and device_status */
+				bool fuse_winograd = false; /* cudaContextSetWinogradFusion */
+				DeferredGemm deferred;
 
 				explicit ContextObject(int deviceIndex, bool isDefault);
 				~ContextObject();
@@ -245,6 +260,15 @@ namespace avocado
 						return handle >= 0 and handle_kind(handle) == m_kind and not handle_is_default(handle) and slot < m_slots.size()
 								and m_slots[slot] != nullptr and m_generation[slot] == handle_generation(handle);
 					}
+					/* Calls f(object) for every live object; f must not call back into this pool. */
+					template<class F>
+					void for_each(F &&f)
+					{
+						std::lock_guard<std::mutex> lock(m_mutex);
+						for (auto &slot : m_slots)
+							if (slot != nullptr)
+								f(*slot);
+					}
 					/* Removes the object and returns it so that its destructor runs outside the pool lock. */
 					std::unique_ptr<T> remove(int64_t handle)
 					{
@@ -270,8 +294,15 @@ namespace avocado
 
 			int getNumberOfDevices() noexcept;
 
-			/* Lookups used by the operators; each throws std::invalid_argument on a handle that is not live. */
+			/* Lookups used by the operators; each throws std::invalid_argument on a handle that is not live.
+			 * getContext first launches a batched GEMM the context may be holding back (see DeferredGemm), so every
+			 * entry point sees the context as if nothing had been deferred; getContextKeepDeferred is for the two
+			 * entry points that look at the held-back call themselves. */
 			ContextObject& getContext(avContextDescriptor_t handle);
+			ContextObject& getContextKeepDeferred(avContextDescriptor_t handle);
+			/* number of contexts currently holding a call back (lets the common path skip the search) */
+			int deferredCount() noexcept;
+			void noteDeferred(int delta) noexcept;
 			bool isDefault(avContextDescriptor_t handle) noexcept;
 			MemoryObject& getMemory(avMemoryDescriptor_t handle);
 			TensorObject& getTensor(avTensorDescriptor_t handle);

@@ -9,8 +9,8 @@
  *   y(tile) = A^T M A   (A^T is 2 x 4)      =>      y[a][b] = sum_nu ( sum_xi A^T[a][xi] M[xi][nu] ) A^T[b][nu]
  *
  * so the planes are taken in four groups of constant nu.  One work item = 128 tiles x 64 filters:
- *   warp 0      TMA producer: for nu, xi, channel block: V[xi*4+nu] (128 tiles x 64 channels) and U[xi*4+nu]
- *               (64 filters x 64 channels) into a ring of 128-byte-swizzled stages
+ *   warp 0      TMA producer: for nu, channel block: the four planes V[xi*4+nu] (128 tiles x 64 channels each) and
+ *               U[xi*4+nu] (64 filters x 64 channels each) into one of two 128-byte-swizzled stages
  *   warp 1      one thread issues tcgen05.mma (M = 128, N = 64) into the group's four accumulators (4 x 64 TMEM columns);
  *               two groups fit TMEM, so the next group is contracted while the previous one is drained
  *   warps 2..9  drain a group (tcgen05.ld), apply the column transform over xi, and add the group's contribution to
@@ -38,10 +38,15 @@ namespace
 	constexpr int kBlockTiles = 128;
 	constexpr int kBlockFilters = 64;
 	constexpr int kBlockChannels = 64; /* 128 bytes of float16 */
-	constexpr int kStages = 8;
+	/* A stage holds the operands of all four planes of a group for one block of 64 channels, so that consecutive MMAs go
+	 * to different accumulators: an MMA that accumulates into the tile the previous one wrote waits for it (about 200
+	 * cycles), and the four MMAs of one plane issued in a row set the pace of the whole kernel (about 700 cycles per
+	 * 24 KB of operands, measured).  Interleaved, a plane's accumulator is touched again only three MMAs later. */
+	constexpr int kStagePlanes = 4;
+	constexpr int kStages = 2;
 	constexpr int kABytes = kBlockTiles * 128;
 	constexpr int kBBytes = kBlockFilters * 128;
-	constexpr int kStageBytes = kABytes + kBBytes;
+	constexpr int kStageBytes = kStagePlanes * (kABytes + kBBytes);
 	constexpr int kSmemBytes = kStages * kStageBytes + 1024;
 	constexpr int kGroupColumns = 4 * kBlockFilters; /* four planes of one group */
 	constexpr int kTmemColumns = 2 * kGroupColumns;
@@ -231,27 +236,30 @@ namespace
 					/* plain nested counters: this thread's own instruction latency bounds how fast stages can be issued, and an
 					 * integer division costs it more than the copy it is about to start */
 					for (int nu = 0; nu < 4 and ok; nu++)
-						for (int xi = 0; xi < 4 and ok; xi++)
-							for (int cb = 0; cb < p.channel_blocks; cb++)
+						for (int cb = 0; cb < p.channel_blocks; cb++)
+						{
+							if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
+							{
+								umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
+								ok = false;
+								break;
+							}
+							uint8_t *a_dst = smem + stage * kStageBytes;
+							uint8_t *b_dst = a_dst + kStagePlanes * kABytes;
+							umma::mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+#pragma unroll
+							for (int xi = 0; xi < kStagePlanes; xi++)
 							{
 								const int plane = xi * 4 + nu;
-								if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
-								{
-									umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
-									ok = false;
-									break;
-								}
-								uint8_t *a_dst = smem + stage * kStageBytes;
-								uint8_t *b_dst = a_dst + kABytes;
-								umma::mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-								umma::tma_load_3d(a_dst, &mapV, &full_bar[stage], cb * kBlockChannels, tb * kBlockTiles, plane);
-								umma::tma_load_3d(b_dst, &mapU, &full_bar[stage], cb * kBlockChannels, fb * kBlockFilters, plane);
-								if (++stage == kStages)
-								{
-									stage = 0;
-									phase ^= 1u;
-								}
+								umma::tma_load_3d(a_dst + xi * kABytes, &mapV, &full_bar[stage], cb * kBlockChannels, tb * kBlockTiles, plane);
+								umma::tma_load_3d(b_dst + xi * kBBytes, &mapU, &full_bar[stage], cb * kBlockChannels, fb * kBlockFilters, plane);
 							}
+							if (++stage == kStages)
+							{
+								stage = 0;
+								phase ^= 1u;
+							}
+						}
 				}
 			}
 		}
@@ -278,27 +286,31 @@ namespace
 							break;
 						}
 						umma::tcgen05_fence_after();
-						for (int xi = 0; xi < 4 and ok; xi++)
+						const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kGroupColumns);
+						for (int cb = 0; cb < p.channel_blocks; cb++)
 						{
-							const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kGroupColumns + xi * kBlockFilters);
-							for (int cb = 0; cb < p.channel_blocks; cb++)
+							if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
 							{
-								if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
-								{
-									umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
-									ok = false;
-									break;
-								}
-								umma::tcgen05_fence_after();
-								/* the address field counts 16-byte units, so a stage further on is a plain addition */
-								const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kStageBytes / 16));
-								umma::mma_f16_k4(tmem_d, a_desc, a_desc + kABytes / 16, idesc, cb != 0);
-								umma::mma_commit(&empty_bar[stage]);
-								if (++stage == kStages)
-								{
-									stage = 0;
-									phase ^= 1u;
-								}
+								umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
+								ok = false;
+								break;
+							}
+							umma::tcgen05_fence_after();
+							/* the address field counts 16-byte units; a 16-element step along the contraction is 32 bytes of the
+							 * 128-byte swizzle row.  Contraction step outermost, plane innermost. */
+							const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kStageBytes / 16));
+							const uint64_t b_desc = a_desc + static_cast<uint64_t>(kStagePlanes * (kABytes / 16));
+#pragma unroll
+							for (int ks = 0; ks < kBlockChannels / 16; ks++)
+#pragma unroll
+								for (int xi = 0; xi < kStagePlanes; xi++)
+									umma::mma_f16(tmem_d + static_cast<uint32_t>(xi * kBlockFilters), a_desc + static_cast<uint64_t>(xi * (kABytes / 16) + 2 * ks),
+											b_desc + static_cast<uint64_t>(xi * (kBBytes / 16) + 2 * ks), idesc, cb != 0 or ks != 0);
+							umma::mma_commit(&empty_bar[stage]);
+							if (++stage == kStages)
+							{
+								stage = 0;
+								phase ^= 1u;
 							}
 						}
 						if (ok)

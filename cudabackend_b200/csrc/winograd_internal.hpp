@@ -34,6 +34,15 @@ namespace bk
 			const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const avocado::backend::b200::TensorObject &c, void *cPtr,
 			int *deviceStatus);
 
+	/* Holds the call back instead of launching it when the context has fusion switched on and the call is the contraction
+	 * of an F(4x4,3x3) pipeline that the fused contraction + output transform kernel could take over; returns whether it did. */
+	bool defer_gemm_batched(avocado::backend::b200::ContextObject &ctx, bool transA, bool transB, const void *alpha,
+			const avocado::backend::b200::TensorObject &a, const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const void *beta,
+			const avocado::backend::b200::TensorObject &c, void *cPtr);
+
+	/* Launches the batched GEMM the context is holding back, if any (see DeferredGemm in objects.hpp). */
+	avocado::backend::avStatus_t flush_deferred_gemm(avocado::backend::b200::ContextObject &ctx);
+
 	/* Device address of the error word inside the fixed scratch array of cudaConvolutionWinogradFusedForwardNoAlloc on
 	 * this device, or null while no call of that entry point has resolved the array's address there yet. */
 	int* no_alloc_status_word(int device) noexcept;

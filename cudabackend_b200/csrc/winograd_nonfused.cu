@@ -21,6 +21,7 @@
 #include "winograd_tables.cuh"
 #include "winograd_f43.cuh"
 #include "winograd_internal.hpp"
+#include "conv_kernels.hpp"
 
 #include <cuda_runtime_api.h>
 
@@ -866,10 +867,37 @@ namespace avocado
 				const void *alpha2, const avTensorDescriptor_t zDesc, const avMemoryDescriptor_t zMem, const void *beta, avActivationType_t activation)
 		{
 			AVOCADO_API_BEGIN
-				ContextObject &ctx = getContext(context);
+				ContextObject &ctx = getContextKeepDeferred(context);
 				const ConvolutionObject &conv = getConvolution(config);
 				(void) bDesc;
 				(void) zDesc;
+				if (ctx.deferred.valid)
+				{
+					/* the context is holding back a batched GEMM: if its result is exactly the tensor this call transforms, one
+					 * kernel does the contraction and the transform and the products are never written; anything else launches
+					 * the GEMM first */
+					const DeferredGemm &d = ctx.deferred;
+					const TensorObject &w = getTensor(wDesc);
+					const TensorObject &m = getTensor(matricesDesc);
+					const TensorObject &y = getTensor(yDesc);
+					void *yPtr = getPointer(yMem);
+					if (transformSize == 4 and w.nb_dims == 4 and is_conv(3, w) and getPointer(matricesMem) == d.cPtr and m.nb_dims == 3 and m.dtype == d.c.dtype
+							and m.dims[0] == d.c.dims[0] and m.dims[1] == d.c.dims[1] and m.dims[2] == d.c.dims[2] and y.dtype == w.dtype and yPtr != nullptr
+							and (bMem == AVOCADO_INVALID_DESCRIPTOR or getTensor(bDesc).dtype == AVOCADO_DTYPE_FLOAT32))
+					{
+						const avStatus_t fused = bk::winograd_f43_contract_output(ctx, d.a, d.aPtr, d.b, d.bPtr, y, yPtr, getPointer(bMem), getPointer(zMem),
+								alpha1, alpha2, beta, activation, ctx.getDeviceStatus());
+						if (fused != AVOCADO_STATUS_NOT_SUPPORTED)
+						{
+							ctx.deferred.valid = false;
+							noteDeferred(-1);
+							return fused;
+						}
+					}
+					const avStatus_t flushed = bk::flush_deferred_gemm(ctx);
+					if (flushed != AVOCADO_STATUS_SUCCESS)
+						return flushed;
+				}
 				return bk::winograd_output_transform(ctx, conv, transformSize, getTensor(wDesc), alpha1, getTensor(matricesDesc), getPointer(matricesMem), getTensor(yDesc), getPointer(yMem),
 						getPointer(bMem), alpha2, getPointer(zMem), beta, activation);
 			AVOCADO_API_END

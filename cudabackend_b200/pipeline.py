@@ -70,6 +70,10 @@ class WinogradNonFused:
         self.z = api.DeviceTensor((self.n, self.h, self.w, self.k), self.dtype, self.x.mem.device)
         return self.z.upload(self.ctx, values)
 
+    def enable_fusion(self, enabled=True):
+        """Switches the context's Winograd fusion: the contraction and the output transform of forward() then run as one kernel."""
+        self.ctx.set_winograd_fusion(enabled)
+
     # ---- individual stages --------------------------------------------------------------------------------
     def weight_transform(self, rotated=False, ctx=None):
         conv = self.conv_rotated if rotated else self.conv

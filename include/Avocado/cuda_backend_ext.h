@@ -52,6 +52,18 @@ DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, 
  * entry point has been made on the device.  No counterpart in the reference. */
 DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTestNoAlloc(avContextDescriptor_t context, int limitMicroseconds);
 
+/* Switches fusion of the non-fused F(4x4,3x3) Winograd pipeline on (enabled != 0) or off for one context.  The call
+ * sequence of the reference stays as it is (ref app/CudaBackend.cu:401-420: weight transform, input transform,
+ * cudaGemmBatched, cudaWinogradOutputTransform).  With fusion on, a cudaGemmBatched call that is the contraction of such a
+ * pipeline (36 planes, (N, T), float16 / bfloat16, alpha 1, beta 0) is held back; if the next call on the context is the
+ * cudaWinogradOutputTransform of exactly the tensor it was to write, ONE kernel contracts and transforms and the
+ * transform-domain products are NEVER WRITTEN to the caller's workspace -- the workspace keeps whatever it held.  That
+ * is the one observable difference, and the reason fusion is opt-in.  Any other call on the context (another operator, a
+ * copy, a synchronisation, the end of a capture, destruction of the context or of any memory descriptor) launches the
+ * held-back GEMM first, so nothing else can tell that it was deferred.  Default contexts cannot fuse.  No counterpart in
+ * the reference, whose two calls always run as two kernels (src/gemm.cpp:126-209, src/winograd_nonfused.cu:703-777). */
+DLL_PUBLIC avStatus_t cudaContextSetWinogradFusion(avContextDescriptor_t context, int enabled);
+
 /* Orders two contexts on the device without blocking the host: everything enqueued on `waiting` after this call runs
  * after everything enqueued on `signalling` before it.  The reference has only cudaSynchronizeWithContext, which blocks
  * the calling thread; with this a caller can run independent steps on two contexts (for instance the weight transform
