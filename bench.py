@@ -57,6 +57,10 @@ TOLERANCE = {"float32": 1e-3, "float16": 1e-2, "bfloat16": 1e-2}
 F43_FLOAT16_DOMAIN_BOUND = 8e-2
 
 
+# --fusion -> flags of cudaContextSetWinogradFusion (AVOCADO_WINOGRAD_FUSE_WEIGHTS = 1, AVOCADO_WINOGRAD_FUSE_OUTPUT = 2)
+FUSION = {"none": 0, "weights": 1, "output": 2, "all": 3}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -232,15 +236,17 @@ class Workload:
     """One buffer set (context + tensors) of the configured convolution; several are rotated so that a step never
     finds its inputs in L2 from the step before."""
 
-    def __init__(self, cfg, device, matrices_dtype, data, fusion=False, keep_inputs=False):
+    def __init__(self, cfg, device, matrices_dtype, data, fusion=0, keep_inputs=False):
         from cudabackend_b200 import api, pipeline
         self.api = api
         self.cfg = cfg
         self.ctx = api.Context(device)
         self.fusion = fusion
+        self.fuse_output = bool(fusion & api.FUSE_OUTPUT)
         if fusion:
-            # opt-in of the library: cudaGemmBatched + cudaWinogradOutputTransform of the pipeline run as one kernel
-            self.ctx.set_winograd_fusion(True)
+            # opt-ins of the library: the weight transform rides in the input transform's launch (FUSE_WEIGHTS) and
+            # cudaGemmBatched + cudaWinogradOutputTransform run as one kernel (FUSE_OUTPUT)
+            self.ctx.set_winograd_fusion(fusion)
         n, h, w, c, k = cfg["n"], cfg["h"], cfg["w"], cfg["c"], cfg["k"]
         kind = cfg["kind"]
         stored = {}
@@ -277,18 +283,19 @@ class Workload:
         # kernels of this library launched per step: forward chain 4; dX chain 5 (its (N,N) contraction transposes U first);
         # dW chain 4 (gradient transform, split contraction + fixed-order reduction, update transform; V comes from the
         # forward pass); one-call Winograd 3 (weight, input, contraction + output)
-        return {"winograd_nonfused": 3 if self.fusion else 4, "training": 4 + 5 + 4, "winograd_fused": 3, "implicit_gemm": 1}[self.cfg["kind"]]
+        nonfused = 4 - (1 if self.fusion & 1 else 0) - (1 if self.fusion & 2 else 0)
+        return {"winograd_nonfused": nonfused, "training": 4 + 5 + 4, "winograd_fused": 2, "implicit_gemm": 1}[self.cfg["kind"]]
 
     def stages(self):
         """(name, callable) pairs making up one step, in issue order."""
         kind = self.cfg["kind"]
         p = self.p
-        if kind == "winograd_nonfused" and self.fusion:
-            return [("weight_transform", p.weight_transform), ("input_transform", p.input_transform),
-                    ("gemm_output_fused", lambda: (p.gemm(p.v, p.u, p.m, False, True), p.output_transform()))]
         if kind == "winograd_nonfused":
-            return [("weight_transform", p.weight_transform), ("input_transform", p.input_transform),
-                    ("gemm", lambda: p.gemm(p.v, p.u, p.m, False, True)), ("output_transform", p.output_transform)]
+            first = ([("weight_input_transform", lambda: (p.weight_transform(), p.input_transform()))] if self.fusion & 1 else
+                     [("weight_transform", p.weight_transform), ("input_transform", p.input_transform)])
+            if self.fuse_output:
+                return first + [("gemm_output_fused", lambda: (p.gemm(p.v, p.u, p.m, False, True), p.output_transform()))]
+            return first + [("gemm", lambda: p.gemm(p.v, p.u, p.m, False, True)), ("output_transform", p.output_transform)]
         if kind == "training":
             return [("forward", p.forward), ("backward_weights", lambda: p.backward_weights(reuse_v=True)), ("backward_data", p.backward_data)]
         if kind == "winograd_fused":
@@ -346,6 +353,7 @@ def stage_bytes(cfg, matrices_dtype):
     mb = elem_size(matrices_dtype)
     t = n * ((h + 3) // 4) * ((w + 3) // 4)
     return {"weight_transform": 9 * k * c * b + 36 * k * c * mb, "input_transform": n * h * w * c * b + 36 * t * c * mb,
+            "weight_input_transform": 9 * k * c * b + 36 * k * c * mb + n * h * w * c * b + 36 * t * c * mb,
             "gemm": 36 * t * c * mb + 36 * k * c * mb + 36 * t * k * mb, "output_transform": 36 * t * k * mb + n * h * w * k * b,
             "gemm_output_fused": 36 * t * c * mb + 36 * k * c * mb + n * h * w * k * b,
             "gemm_flops": 2.0 * 36 * t * c * k}
@@ -358,7 +366,7 @@ def algorithmic_bytes(cfg, matrices_dtype, fusion=False):
     kind = cfg["kind"]
     if kind == "winograd_nonfused":
         sb = stage_bytes(cfg, matrices_dtype)
-        if fusion:
+        if fusion & 2:
             return sb["weight_transform"] + sb["input_transform"] + sb["gemm_output_fused"]
         return sb["weight_transform"] + sb["input_transform"] + sb["gemm"] + sb["output_transform"]
     if kind == "winograd_fused":
@@ -437,7 +445,7 @@ def library_peaks(device):
 class Measurement:
     """Buffer sets, graphs and timing of one (configuration, matrices dtype, per-GPU batch) on one GPU."""
 
-    def __init__(self, args, config_id, cfg, matrices_dtype, rank, world, local_rank, seed_offset=0, fusion=False):
+    def __init__(self, args, config_id, cfg, matrices_dtype, rank, world, local_rank, seed_offset=0, fusion=0):
         import torch
         self.torch = torch
         self.args = args
@@ -448,7 +456,10 @@ class Measurement:
         self.matrices = matrices_dtype if cfg["kind"] in ("winograd_nonfused", "training") else None
         if cfg["kind"] == "training":
             self.matrices = "float32"
-        self.fusion = fusion and cfg["kind"] == "winograd_nonfused" and self.matrices in ("float16", "bfloat16")
+        self.fusion = int(fusion) if cfg["kind"] == "winograd_nonfused" else 0
+        if self.matrices not in ("float16", "bfloat16"):
+            self.fusion &= 1  # the one-kernel contraction + output transform exists for 16-bit transform-domain tensors
+        self.fuse_output = bool(self.fusion & 2)
         self.data = synthetic(cfg, seed_offset=seed_offset)
         self.rotation = args.rotation
         self.sets = [Workload(cfg, local_rank, self.matrices, self.data, fusion=self.fusion, keep_inputs=(i == 0)) for i in range(self.rotation)]
@@ -753,20 +764,20 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
     if kind == "winograd_nonfused":
         sb = stage_bytes(cfg, matrices)
         total = algorithmic_bytes(cfg, matrices, m.fusion)
-        dominant = "gemm_output_fused" if m.fusion else "gemm"
-        gemm_s = stage_ms[dominant] * 1e-3
+        dominant = "gemm_output_fused" if m.fuse_output else "gemm"
+        gemm_s = stage_ms.get(dominant, ms_per_step) * 1e-3
         achieved = sb[dominant] / gemm_s / 1e9
-        if m.fusion:
+        if m.fuse_output:
             name = "kernel_f43_contract_output (transform-domain contraction + output transform in one kernel; M stays in TMEM)"
         else:
             name = ("kernel_gemm_nt_tc" if matrices != "float32" else "kernel_gemm_nt_tf32x3") + " (transform-domain batched GEMM)"
         rec = {"kernel": name, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-               "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get((m.config_id, matrices, m.fusion)), "algorithmic_bytes": sb[dominant],
+               "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get((m.config_id, matrices, m.fuse_output)), "algorithmic_bytes": sb[dominant],
                "device_copy_of_same_bytes": copy_reference, "peak_source": peaks["source"], "tensor_tflops": sb["gemm_flops"] / gemm_s / 1e12,
                "tensor_frac": sb["gemm_flops"] / gemm_s / 1e12 / peaks["bf16_tflops"],
                "pipeline": {"algorithmic_bytes": total, "achieved": total / step_s / 1e9, "frac": total / step_s / 1e9 / peaks["hbm_gbs"]}}
-        if m.fusion:
-            unfused = algorithmic_bytes(cfg, matrices, False)
+        if m.fuse_output:
+            unfused = algorithmic_bytes(cfg, matrices, 0)
             rec["pipeline"]["unfused_algorithmic_bytes"] = unfused
             rec["pipeline"]["frac_on_unfused_bytes"] = unfused / step_s / 1e9 / peaks["hbm_gbs"]
         names = [n for n in stage_ms if n in sb]
@@ -802,7 +813,7 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
 
 
 def sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_peaks, sampler, per_gpu_batch=None, steps_per_graph=1,
-               want_parity=True, want_sustained=True, want_stages=True, fusion=False):
+               want_parity=True, want_sustained=True, want_stages=True, fusion=0):
     """Device-timed record of one configuration: value, roofline, parity, sustained."""
     cfg = dict(CONFIGS[config_id])
     if per_gpu_batch is not None:
@@ -823,7 +834,7 @@ def sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_pe
     if stage_ms:
         record["stage_ms"] = stage_ms
     if rank == 0:
-        record["roofline"] = roofline_record(m, ms_per_step, stage_ms or {"gemm": ms_per_step}, peaks, lib_peaks)
+        record["roofline"] = roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks)
     if want_sustained:
         m.capture(steps_per_graph)
         record["sustained"] = m.sustained(args.sustained_seconds, sampler if rank == 0 else None)
@@ -973,14 +984,14 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
 
     # ---- headline: the configured workload, every rank its own batch ---------------------------------------
     matrices_dtype = args.matrices or cfg["dtype"]
-    m = Measurement(args, args.config, cfg, matrices_dtype, rank, world, local_rank, seed_offset=rank, fusion=not args.no_fusion)
+    m = Measurement(args, args.config, cfg, matrices_dtype, rank, world, local_rank, seed_offset=rank, fusion=FUSION[args.fusion])
     m.capture(1)
     elapsed_ms, done, clocks, wall_ms = m.timed(args.steps, args.warmup, sampler if rank == 0 else None)
     ms_per_step = elapsed_ms / done
     stage_ms = m.stage_times(max(20, min(args.steps, 200)))
     copy_reference = None
     if cfg["kind"] == "winograd_nonfused":
-        copy_reference = m.copy_reference(stage_bytes(cfg, m.matrices)["gemm_output_fused" if m.fusion else "gemm"], max(20, min(args.steps, 200)))
+        copy_reference = m.copy_reference(stage_bytes(cfg, m.matrices)["gemm_output_fused" if m.fuse_output else "gemm"], max(20, min(args.steps, 200)))
     m.check_status()
     parity = None
     if rank == 0 and not args.no_parity:
@@ -1009,14 +1020,17 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                                                "int8": "s8 (s32 accumulate)"}[cfg["dtype"]],
                 "data": "synthetic",
                 "config": {"workload": cfg["name"], "per_gpu_batch": cfg["n"], "global_batch": cfg["n"] * world, "matrices_dtype": m.matrices,
-                           "fusion": ("cudaContextSetWinogradFusion on: cudaGemmBatched + cudaWinogradOutputTransform run as one kernel, M is not written"
-                                      if m.fusion else "off: every call is its own kernel"),
+                           "fusion": {0: "off: every call is its own kernel",
+                                      1: "cudaContextSetWinogradFusion(FUSE_WEIGHTS): the weight transform rides in the input transform's launch",
+                                      2: "cudaContextSetWinogradFusion(FUSE_OUTPUT): cudaGemmBatched + cudaWinogradOutputTransform run as one kernel, M is not written",
+                                      3: "cudaContextSetWinogradFusion(FUSE_WEIGHTS | FUSE_OUTPUT): weight transform inside the input transform's launch; "
+                                         "cudaGemmBatched + cudaWinogradOutputTransform as one kernel, M is not written"}[m.fusion],
                            "l2": "rotating %d buffer sets; each set's working set is re-read only after %d other steps" % (m.rotation, m.rotation - 1),
                            "parallelism": "batch sharded, dp%d: every rank runs the configuration's batch (weak scaling); the split of the "
                                           "configuration's own batch over the ranks is under `sharded`" % world},
                 "images_per_s": cfg["n"] * world / (ms_per_step * 1e-3), "host_wall_ms_per_step": wall_ms / done,
                 "e2e": e2e, "gpu_launches": launches, "launch_mode": launch_mode(args), "stage_ms": stage_ms, "clocks": clocks}
-        roof = roofline_record(m, ms_per_step, stage_ms or {"gemm": ms_per_step}, peaks, lib_peaks, copy_reference)
+        roof = roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference)
         line["roofline"] = roof
         if "stage_gbs" in roof:
             line["stage_gbs"] = roof["stage_gbs"]
@@ -1051,7 +1065,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                 first, last = sharding.shard_bounds(CONFIGS[config_id]["n"], world, rank)
                 record = sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_peaks, sampler, per_gpu_batch=last - first,
                                     steps_per_graph=args.rotation, want_parity=False, want_sustained=False, want_stages=False,
-                                    fusion=(config_id == 2 and not args.no_fusion))
+                                    fusion=(FUSION[args.fusion] if config_id == 2 else 0))
                 if rank == 0:
                     record["scaling"] = "strong"
                     record["global_batch"] = CONFIGS[config_id]["n"]
@@ -1093,8 +1107,10 @@ def main():
     parser.add_argument("--only-headline", action="store_true", help="skip the sub-records of the other configurations")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     parser.add_argument("--no-parity", action="store_true", help="skip the comparison of the outputs with the CPU oracle")
-    parser.add_argument("--no-fusion", action="store_true",
-                        help="keep cudaGemmBatched and cudaWinogradOutputTransform as two kernels (the library's default without the opt-in)")
+    parser.add_argument("--fusion", default="weights", choices=sorted(FUSION),
+                        help="cudaContextSetWinogradFusion flags of the non-fused pipeline: none (every call its own kernel, the library's default), "
+                             "weights (the weight transform rides in the input transform's launch), output (contraction + output transform as one "
+                             "kernel, M not written), all")
     parser.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a captured graph")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -22,6 +22,7 @@ CONVOLUTION_MODE, CROSS_CORRELATION_MODE = 0, 1
 GEMM_N, GEMM_T = 0, 1
 INVALID = -1
 NO_ALLOC_SCRATCH_BYTES = 8 * 1024 * 1024  # AVOCADO_NO_ALLOC_SCRATCH_BYTES
+FUSE_WEIGHTS, FUSE_OUTPUT = 1, 2  # AVOCADO_WINOGRAD_FUSE_*
 
 _H = ctypes.c_int64  # every descriptor handle
 _I64 = ctypes.c_int64
@@ -184,9 +185,13 @@ class Context:
         call("cudaGetLastDeviceStatus", self.handle, ctypes.byref(r))
         return int(r.value)
 
-    def set_winograd_fusion(self, enabled):
-        """Lets cudaGemmBatched + cudaWinogradOutputTransform of an F(4x4,3x3) pipeline run as one kernel (the products M are then not written)."""
-        call("cudaContextSetWinogradFusion", self.handle, 1 if enabled else 0)
+    def set_winograd_fusion(self, flags):
+        """flags: 0, FUSE_WEIGHTS (the weight transform rides in the input transform's launch), FUSE_OUTPUT (cudaGemmBatched +
+        cudaWinogradOutputTransform of an F(4x4,3x3) pipeline run as one kernel; the products M are then not written), or both.
+        True means both."""
+        if flags is True:
+            flags = FUSE_WEIGHTS | FUSE_OUTPUT
+        call("cudaContextSetWinogradFusion", self.handle, int(flags))
 
     def wait_for(self, other):
         """Work enqueued on this context from now on runs after the work already enqueued on `other` (no host blocking)."""

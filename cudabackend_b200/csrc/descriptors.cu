@@ -237,6 +237,9 @@ namespace avocado
 			ContextObject& getContext(avContextDescriptor_t handle)
 			{
 				ContextObject &ctx = getContextKeepDeferred(handle);
+				/* in the order the calls were made: a weight transform can only have been held back before a GEMM */
+				if (ctx.deferred_weights.valid and bk::flush_deferred_weights(ctx) != AVOCADO_STATUS_SUCCESS)
+					throw std::runtime_error("the weight transform held back on this context failed to launch");
 				if (ctx.deferred.valid and bk::flush_deferred_gemm(ctx) != AVOCADO_STATUS_SUCCESS)
 					throw std::runtime_error("the batched GEMM held back on this context failed to launch");
 				return ctx;
@@ -418,8 +421,10 @@ namespace avocado
 			std::unique_ptr<ContextObject> object = contextPool().remove(desc);
 			if (object == nullptr)
 				return AVOCADO_STATUS_BAD_PARAM;
+			if (object->deferred_weights.valid)
+				bk::flush_deferred_weights(*object); /* the caller asked for these results: they are not dropped with the context */
 			if (object->deferred.valid)
-				bk::flush_deferred_gemm(*object); /* the caller asked for that product: it is not dropped with the context */
+				bk::flush_deferred_gemm(*object);
 			object.reset();
 			return AVOCADO_STATUS_SUCCESS;
 		}
@@ -508,6 +513,8 @@ namespace avocado
 			if (deferredCount() > 0)
 				contextPool().for_each([](ContextObject &ctx)
 				{
+					if (ctx.deferred_weights.valid)
+						bk::flush_deferred_weights(ctx);
 					if (ctx.deferred.valid)
 						bk::flush_deferred_gemm(ctx);
 				});
@@ -894,13 +901,14 @@ namespace avocado
 			AVOCADO_API_END
 		}
 
-		avStatus_t cudaContextSetWinogradFusion(avContextDescriptor_t context, int enabled)
+		avStatus_t cudaContextSetWinogradFusion(avContextDescriptor_t context, int flags)
 		{
 			AVOCADO_API_BEGIN
-				if (isDefault(context))
+				if (isDefault(context) or (flags & ~(AVOCADO_WINOGRAD_FUSE_WEIGHTS | AVOCADO_WINOGRAD_FUSE_OUTPUT)) != 0)
 					return AVOCADO_STATUS_BAD_PARAM;
 				ContextObject &ctx = getContext(context); /* launches whatever was held back under the old setting */
-				ctx.fuse_winograd = (enabled != 0);
+				ctx.fuse_weights = (flags & AVOCADO_WINOGRAD_FUSE_WEIGHTS) != 0;
+				ctx.fuse_winograd = (flags & AVOCADO_WINOGRAD_FUSE_OUTPUT) != 0;
 				return AVOCADO_STATUS_SUCCESS;
 			AVOCADO_API_END
 		}

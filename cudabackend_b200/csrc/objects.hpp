@@ -182,6 +182,19 @@ namespace avocado
 				void *cPtr = nullptr;
 			};
 
+			/* A cudaWinogradWeightTransform call (3x3 kernel) that a context with Winograd fusion switched on has accepted but
+			 * not launched yet: if the next call on the context is an input transform that the TMA-staged kernel takes, the
+			 * weight transform rides along in that launch; anything else launches it first as a kernel of its own. */
+			struct DeferredWeightTransform
+			{
+				bool valid = false;
+				ConvolutionObject conv;
+				int transform_size = 0;
+				TensorObject w, u;
+				const void *wPtr = nullptr;
+				void *uPtr = nullptr;
+			};
+
 			/* One stream on one device, a grow-only scratch buffer and a device-resident error word that kernels
 			 * with bounded waits set when a wait runs out. */
 			struct ContextObject
@@ -194,8 +207,10 @@ namespace avocado
 				int *device_status = nullptr;
 				cudaEvent_t order_event = nullptr; /* recorded on this stream when another context waits for this one */
 				std::mutex lazy_mutex; /* guards the first allocation of workspace and device_status */
-				bool fuse_winograd = false; /* cudaContextSetWinogradFusion */
+				bool fuse_winograd = false; /* cudaContextSetWinogradFusion, AVOCADO_WINOGRAD_FUSE_OUTPUT: hold cudaGemmBatched back */
+				bool fuse_weights = false; /* AVOCADO_WINOGRAD_FUSE_WEIGHTS: hold cudaWinogradWeightTransform back */
 				DeferredGemm deferred;
+				DeferredWeightTransform deferred_weights;
 
 				explicit ContextObject(int deviceIndex, bool isDefault);
 				~ContextObject();

@@ -21,6 +21,7 @@
 
 #include "device_utils.cuh"
 #include "umma.cuh"
+#include "winograd_tables.cuh"
 
 namespace f43
 {
@@ -217,6 +218,52 @@ namespace f43
 #define F43_OUT_BLOCKS 3
 #endif
 
+	/* A weight transform that rides along with an input-transform launch: the first `ctas` blocks of the grid compute
+	 * U = G w G^T (3x3 kernels, two channels per thread) instead of input strips.  The transform of 74 KB of weights is
+	 * a few microseconds of launch latency as a kernel of its own and nothing inside a launch that is running anyway.
+	 * ctas == 0 means no job. */
+	struct WeightJob
+	{
+			const void *weights; /* [K, 3, 3, C] */
+			void *matrices; /* [(TS + 2)^2, K, C] */
+			int filters, channels;
+			int invert; /* 180 degree rotation of the kernel (AVOCADO_CROSS_CORRELATION_MODE) */
+			int ctas;
+	};
+
+	/* same arithmetic as kernel_weight_transform of winograd_nonfused.cu (winograd::transform_2d on the compile-time
+	 * tables), so the result does not depend on which launch computed it */
+	template<int TS, typename T, typename MT>
+	__device__ __forceinline__ void weight_transform_pairs(const WeightJob &job, int cta, int threads)
+	{
+		using M = winograd::Matrix<winograd::Transform::Weight, TS, 3>;
+		const int cpairs = job.channels / 2;
+		const long long total = static_cast<long long>(job.filters) * cpairs;
+		const T *weights = reinterpret_cast<const T*>(job.weights);
+		MT *matrices = reinterpret_cast<MT*>(job.matrices);
+		for (long long g = static_cast<long long>(cta) * threads + threadIdx.x; g < total; g += static_cast<long long>(job.ctas) * threads)
+		{
+			const int c0 = static_cast<int>(g % cpairs) * 2;
+			const int k = static_cast<int>(g / cpairs);
+			float in[2][9];
+#pragma unroll
+			for (int i = 0; i < 9; i++)
+			{
+				const float2 v = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::type*>(weights + (static_cast<size_t>(k) * 9 + i) * job.channels + c0));
+				const int dst = job.invert ? (8 - i) : i;
+				in[0][dst] = v.x;
+				in[1][dst] = v.y;
+			}
+			float out[2][M::Rows * M::Rows];
+			winograd::transform_2d<M, float>(in[0], out[0]);
+			winograd::transform_2d<M, float>(in[1], out[1]);
+#pragma unroll
+			for (int p = 0; p < M::Rows * M::Rows; p++)
+				*reinterpret_cast<typename Pair<MT>::type*>(matrices + (static_cast<size_t>(p) * job.filters + k) * job.channels + c0) = Pair<MT>::pack(out[0][p],
+						out[1][p]);
+		}
+	}
+
 	struct InputGeometry
 	{
 			int batch, tiles_h, tiles_w, channels;
@@ -233,10 +280,18 @@ namespace f43
 	template<int TS, typename T, typename MT>
 	/* the halo ring (up to 96 KB per block) lets two blocks share an SM: give each the registers of half an SM (no spills) */
 	__global__ void __launch_bounds__(kThreads, 2) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
-			int *deviceStatus)
+			int *deviceStatus, WeightJob weightJob)
 	{
-		using PT = typename Pair<T>::type;
-		using PM = typename Pair<MT>::type;
+		if (static_cast<int>(blockIdx.x) < weightJob.ctas)
+		{
+			/* a block of the weight transform that rides along (see WeightJob) */
+			chain_wait();
+			chain_release();
+			weight_transform_pairs<TS, T, MT>(weightJob, static_cast<int>(blockIdx.x), static_cast<int>(blockDim.x));
+			return;
+		}
+		const int cta = static_cast<int>(blockIdx.x) - weightJob.ctas;
+		const int ncta = static_cast<int>(gridDim.x) - weightJob.ctas;
 		extern __shared__ uint8_t smem_raw[];
 		uint8_t *smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
 		__shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -274,7 +329,7 @@ namespace f43
 		if (tid == 0)
 			for (int i = 0; i < g.stages - 1; i++)
 			{
-				const long long item = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
+				const long long item = static_cast<long long>(cta) + static_cast<long long>(i) * ncta;
 				if (item < g.num_items)
 					issue(static_cast<int>(item), i);
 			}
@@ -282,14 +337,14 @@ namespace f43
 		const size_t plane_stride = static_cast<size_t>(g.nb_tiles) * g.channels;
 		const int row_pitch = g.box_w * kChannelBlock; /* elements of T per box row */
 		int it = 0;
-		for (int item = blockIdx.x; item < g.num_items; item += gridDim.x, it++)
+		for (int item = cta; item < g.num_items; item += ncta, it++)
 		{
 			const int stage = it % g.stages;
 			const uint32_t phase = static_cast<uint32_t>(it / g.stages) & 1u;
 			if (tid == 0)
 			{
 				/* the buffer consumed in the previous iteration was released by the barrier that closed it */
-				const long long next = static_cast<long long>(item) + static_cast<long long>(g.stages - 1) * gridDim.x;
+				const long long next = static_cast<long long>(item) + static_cast<long long>(g.stages - 1) * ncta;
 				if (next < g.num_items)
 					issue(static_cast<int>(next), (it + g.stages - 1) % g.stages);
 				const bool ready = umma::mbar_wait(&full_bar[stage], phase, &abort_flag);

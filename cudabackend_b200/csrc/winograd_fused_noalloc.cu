@@ -175,12 +175,17 @@ namespace avocado
 				const TensorObject v = make_tensor(domain, { planes, static_cast<int>(tiles), channels });
 				const TensorObject m = make_tensor(domain, { planes, static_cast<int>(tiles), filters });
 
-				avStatus_t status = bk::winograd_weight_transform(ctx, conv, 2, w, wPtr, u, u_ptr);
+				bk::WeightRide ride = { wPtr, u_ptr, filters, channels, 2, conv.mode == AVOCADO_CROSS_CORRELATION_MODE, w.dtype, domain };
+				bool ride_taken = false;
+				avStatus_t status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr, status_word, &ride, &ride_taken);
 				if (status != AVOCADO_STATUS_SUCCESS)
 					return status;
-				status = bk::winograd_input_transform(ctx, conv, 2, w, x, xPtr, v, v_ptr, status_word);
-				if (status != AVOCADO_STATUS_SUCCESS)
-					return status;
+				if (not ride_taken)
+				{
+					status = bk::winograd_weight_transform(ctx, conv, 2, w, wPtr, u, u_ptr);
+					if (status != AVOCADO_STATUS_SUCCESS)
+						return status;
+				}
 				if (single_kernel)
 					/* the same single-kernel contraction + output transform the allocating entry point uses */
 					return bk::winograd_f23_contract_output(ctx, args, y.dtype, tiles, v_ptr, u_ptr, alpha1, alpha2, beta, status_word);

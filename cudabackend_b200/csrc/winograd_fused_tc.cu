@@ -9,6 +9,8 @@
  *
  *   U = weight transform(w)        V = input transform(x)        M = V x U^T (tcgen05)        y = output transform(M)
  *
+ * (the first two in one launch: the weight transform is a few blocks at the front of the input transform's grid)
+ *
  * with the bias / z / activation / beta epilogue fused into the output transform.  For float16 / bfloat16 tensors the
  * last two steps are ONE kernel (winograd_fused_f23_tc.cu): M stays in TMEM and is never written to memory.  The transform-domain tensors are
  * internal, so their format is chosen for accuracy: float16 for float16 AND bfloat16 tensors with F(2x2,3x3) (a
@@ -110,12 +112,18 @@ namespace bk
 		const TensorObject v = make_tensor(matrices_type, { planes, static_cast<int>(tiles), args.channels });
 		const TensorObject m = make_tensor(matrices_type, { planes, static_cast<int>(tiles), args.filters });
 
-		avStatus_t status = winograd_weight_transform(ctx, conv, transform_size, w, args.w, u, u_ptr);
+		/* the weight transform rides along with the launch of the input transform when that launch can carry it */
+		WeightRide ride = { args.w, u_ptr, args.filters, args.channels, transform_size, args.rotate_kernel, xType, matrices_type };
+		bool ride_taken = false;
+		avStatus_t status = winograd_input_transform(ctx, conv, transform_size, w, x, args.x, v, v_ptr, nullptr, &ride, &ride_taken);
 		if (status != AVOCADO_STATUS_SUCCESS)
 			return status;
-		status = winograd_input_transform(ctx, conv, transform_size, w, x, args.x, v, v_ptr);
-		if (status != AVOCADO_STATUS_SUCCESS)
-			return status;
+		if (not ride_taken)
+		{
+			status = winograd_weight_transform(ctx, conv, transform_size, w, args.w, u, u_ptr);
+			if (status != AVOCADO_STATUS_SUCCESS)
+				return status;
+		}
 		if (transform_size == 2 and not chained_form_forced())
 		{
 			/* contraction and output transform in one kernel; M is never written */

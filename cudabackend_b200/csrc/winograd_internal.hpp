@@ -13,10 +13,24 @@ namespace bk
 	avocado::backend::avStatus_t winograd_weight_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
 			int transformSize, const avocado::backend::b200::TensorObject &w, const void *wPtr, const avocado::backend::b200::TensorObject &m, void *mPtr);
 
-	/* deviceStatus: where the TMA-staged kernel reports a wait that ran out; null = the context's own status word */
+	/* A weight transform (3x3 kernel) that may ride along with the launch of an input transform instead of being a
+	 * kernel of its own: the first blocks of that launch compute it.  See f43::WeightJob. */
+	struct WeightRide
+	{
+			const void *weights; /* [K, 3, 3, C] */
+			void *matrices; /* [(transformSize + 2)^2, K, C] */
+			int filters, channels, transformSize;
+			bool invert;
+			avocado::backend::avDataType_t weightType, matrixType;
+	};
+
+	/* deviceStatus: where the TMA-staged kernel reports a wait that ran out; null = the context's own status word.
+	 * ride / rideTaken: a weight transform offered to this launch, and whether the launch took it (only the TMA-staged
+	 * kernel can; when it did not, the caller launches the weight transform itself). */
 	avocado::backend::avStatus_t winograd_input_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
 			int transformSize, const avocado::backend::b200::TensorObject &w, const avocado::backend::b200::TensorObject &x, const void *xPtr,
-			const avocado::backend::b200::TensorObject &m, void *mPtr, int *deviceStatus = nullptr);
+			const avocado::backend::b200::TensorObject &m, void *mPtr, int *deviceStatus = nullptr, const WeightRide *ride = nullptr,
+			bool *rideTaken = nullptr);
 
 	avocado::backend::avStatus_t winograd_output_transform(avocado::backend::b200::ContextObject &ctx, const avocado::backend::b200::ConvolutionObject &conv,
 			int transformSize, const avocado::backend::b200::TensorObject &w, const void *alpha1, const avocado::backend::b200::TensorObject &m,
@@ -39,6 +53,9 @@ namespace bk
 	bool defer_gemm_batched(avocado::backend::b200::ContextObject &ctx, bool transA, bool transB, const void *alpha,
 			const avocado::backend::b200::TensorObject &a, const void *aPtr, const avocado::backend::b200::TensorObject &b, const void *bPtr, const void *beta,
 			const avocado::backend::b200::TensorObject &c, void *cPtr);
+
+	/* Launches the weight transform the context is holding back, if any (see DeferredWeightTransform in objects.hpp). */
+	avocado::backend::avStatus_t flush_deferred_weights(avocado::backend::b200::ContextObject &ctx);
 
 	/* Launches the batched GEMM the context is holding back, if any (see DeferredGemm in objects.hpp). */
 	avocado::backend::avStatus_t flush_deferred_gemm(avocado::backend::b200::ContextObject &ctx);

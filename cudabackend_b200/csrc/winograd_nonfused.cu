@@ -440,7 +440,7 @@ namespace
 
 	template<int TS, typename T, typename MT>
 	avStatus_t launch_f43_input(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
-			int *deviceStatus)
+			int *deviceStatus, const bk::WeightRide *ride, bool *rideTaken)
 	{
 		if (cuda_sm_version(ctx.device) != 100 or not config.paddingValueIsZero())
 			return AVOCADO_STATUS_NOT_SUPPORTED;
@@ -497,11 +497,26 @@ namespace
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
 		const int threads = 32 * std::min(8, g.strip_tiles_h * g.strip_tiles_w);
 		const int ctas_per_sm = std::max(1, std::min(4, (220 * 1024) / (smem_bytes + 1024)));
-		const int grid = std::min(g.num_items, ctas_per_sm * sms);
+		/* a weight transform waiting for a launch to ride along with (3x3 kernel, even channel count, aligned pairs) */
+		f43::WeightJob job = { };
+		if (ride != nullptr and ride->transformSize == TS and ride->filters > 0 and ride->channels > 0 and ride->channels % 2 == 0
+				and aligned_to(ride->weights, 2 * sizeof(T)) and aligned_to(ride->matrices, 2 * sizeof(MT)))
+		{
+			job.weights = ride->weights;
+			job.matrices = ride->matrices;
+			job.filters = ride->filters;
+			job.channels = ride->channels;
+			job.invert = ride->invert ? 1 : 0;
+			const long long pairs = static_cast<long long>(ride->filters) * (ride->channels / 2);
+			job.ctas = static_cast<int>(std::min<long long>((pairs + threads - 1) / threads, std::max(1, sms / 4)));
+		}
+		const int grid = std::max(1, std::min(g.num_items, ctas_per_sm * sms - job.ctas)) + job.ctas;
 		const cudaError_t launched = launch_chained(kernel, dim3(grid), dim3(threads), smem_bytes, ctx.getStream(), map, reinterpret_cast<MT*>(matricesPtr), g,
-				deviceStatus != nullptr ? deviceStatus : ctx.getDeviceStatus());
+				deviceStatus != nullptr ? deviceStatus : ctx.getDeviceStatus(), job);
 		if (launched != cudaSuccess)
 			return convertStatus(launched);
+		if (rideTaken != nullptr)
+			rideTaken[0] = job.ctas > 0;
 		return checkForErrors();
 	}
 
@@ -575,10 +590,10 @@ namespace
 	/* float64 has no fast kernel: these wrappers keep the double instantiations out of the fast templates */
 	template<int TS, typename T, typename MT>
 	avStatus_t launch_f43_input_if(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
-			int *deviceStatus)
+			int *deviceStatus, const bk::WeightRide *ride, bool *rideTaken)
 	{
 		if constexpr (sizeof(T) <= 4)
-			return launch_f43_input<TS, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus);
+			return launch_f43_input<TS, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus, ride, rideTaken);
 		else
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 	}
@@ -603,7 +618,8 @@ namespace
 
 	template<typename T, typename MT>
 	avStatus_t launch_input_transform(ContextObject &ctx, const ConvolutionObject &config, const TensorObject &wDesc, const TensorObject &xDesc,
-			const void *xPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize, int *deviceStatus)
+			const void *xPtr, const TensorObject &matricesDesc, void *matricesPtr, int transformSize, int *deviceStatus, const bk::WeightRide *ride,
+			bool *rideTaken)
 	{
 		using CT = typename ComputeType<T>::type;
 		if (xDesc.nb_dims != 4)
@@ -616,8 +632,8 @@ namespace
 			return AVOCADO_STATUS_SUCCESS;
 		if (ks == 3 and sizeof(T) <= 4 and fast_paths_enabled())
 		{
-			const avStatus_t fast = (transformSize == 4) ? launch_f43_input_if<4, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus) :
-					launch_f43_input_if<2, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus);
+			const avStatus_t fast = (transformSize == 4) ? launch_f43_input_if<4, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus, ride, rideTaken) :
+					launch_f43_input_if<2, T, MT>(ctx, config, geo, xPtr, matricesPtr, deviceStatus, ride, rideTaken);
 			if (fast != AVOCADO_STATUS_NOT_SUPPORTED)
 				return fast;
 		}
@@ -765,8 +781,13 @@ namespace bk
 	}
 
 	avStatus_t winograd_input_transform(ContextObject &ctx, const ConvolutionObject &conv, int transformSize, const TensorObject &w, const TensorObject &x, const void *xPtr,
-			const TensorObject &m, void *mPtr, int *deviceStatus)
+			const TensorObject &m, void *mPtr, int *deviceStatus, const WeightRide *ride, bool *rideTaken)
 	{
+		if (rideTaken != nullptr)
+			rideTaken[0] = false;
+		/* the job rides only with a launch of matching types: its tensors have the dtypes of this call's */
+		if (ride != nullptr and (ride->weightType != w.dtype or ride->matrixType != m.dtype))
+			ride = nullptr;
 		if (not tile_config_supported(w, transformSize))
 			return (w.nb_dims != 4) ? AVOCADO_STATUS_BAD_PARAM : AVOCADO_STATUS_NOT_SUPPORTED;
 		if (xPtr == nullptr or mPtr == nullptr)
@@ -778,22 +799,32 @@ namespace bk
 		switch (classify(w.dtype, m.dtype))
 		{
 			case Pairing::F16_F16:
-				return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<half, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			case Pairing::F16_F32:
-				return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<half, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			case Pairing::BF16_BF16:
-				return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<__nv_bfloat16, __nv_bfloat16>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			case Pairing::BF16_F16:
-				return launch_input_transform<__nv_bfloat16, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<__nv_bfloat16, half>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			case Pairing::BF16_F32:
-				return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<__nv_bfloat16, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			case Pairing::F32_F32:
-				return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<float, float>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			case Pairing::F64_F64:
-				return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus);
+				return launch_input_transform<double, double>(ctx, conv, w, x, xPtr, m, mPtr, transformSize, deviceStatus, ride, rideTaken);
 			default:
 				return AVOCADO_STATUS_UNSUPPORTED_DATATYPE;
 		}
+	}
+
+	avStatus_t flush_deferred_weights(ContextObject &ctx)
+	{
+		if (not ctx.deferred_weights.valid)
+			return AVOCADO_STATUS_SUCCESS;
+		const DeferredWeightTransform d = ctx.deferred_weights;
+		ctx.deferred_weights.valid = false;
+		noteDeferred(-1);
+		return winograd_weight_transform(ctx, d.conv, d.transform_size, d.w, d.wPtr, d.u, d.uPtr);
 	}
 
 	avStatus_t winograd_output_transform(ContextObject &ctx, const ConvolutionObject &conv, int transformSize, const TensorObject &w, const void *alpha1, const TensorObject &m,
@@ -846,7 +877,29 @@ namespace avocado
 			AVOCADO_API_BEGIN
 				ContextObject &ctx = getContext(context);
 				const ConvolutionObject &conv = getConvolution(config);
-				return bk::winograd_weight_transform(ctx, conv, transformSize, getTensor(wDesc), getPointer(wMem), getTensor(matricesDesc), getPointer(matricesMem));
+				const TensorObject &w = getTensor(wDesc);
+				const TensorObject &u = getTensor(matricesDesc);
+				const void *wPtr = getPointer(wMem);
+				void *uPtr = getPointer(matricesMem);
+				/* with fusion switched on, a 3x3 weight transform whose arguments are valid is held back: the input transform
+				 * that usually follows carries it in its own launch */
+				if (ctx.fuse_weights and not ctx.is_default and w.nb_dims == 4 and is_conv(3, w) and (transformSize == 2 or transformSize == 4) and wPtr != nullptr
+						and uPtr != nullptr and classify(w.dtype, u.dtype) != Pairing::Unsupported and w.dtype != AVOCADO_DTYPE_FLOAT64 and u.nb_dims == 3
+						and u.dims[0] == (transformSize + 2) * (transformSize + 2) and u.dims[1] == w.dims[0] and u.dims[2] == w.dims[3] and w.dims[0] > 0
+						and w.dims[3] > 0)
+				{
+					DeferredWeightTransform &d = ctx.deferred_weights;
+					d.valid = true;
+					d.conv = conv;
+					d.transform_size = transformSize;
+					d.w = w;
+					d.u = u;
+					d.wPtr = wPtr;
+					d.uPtr = uPtr;
+					noteDeferred(+1);
+					return AVOCADO_STATUS_SUCCESS;
+				}
+				return bk::winograd_weight_transform(ctx, conv, transformSize, w, wPtr, u, uPtr);
 			AVOCADO_API_END
 		}
 
@@ -855,8 +908,33 @@ namespace avocado
 				avMemoryDescriptor_t matricesMem)
 		{
 			AVOCADO_API_BEGIN
-				ContextObject &ctx = getContext(context);
+				ContextObject &ctx = getContextKeepDeferred(context);
 				const ConvolutionObject &conv = getConvolution(config);
+				if (ctx.deferred.valid)
+				{
+					const avStatus_t flushed = bk::flush_deferred_gemm(ctx);
+					if (flushed != AVOCADO_STATUS_SUCCESS)
+						return flushed;
+				}
+				if (ctx.deferred_weights.valid)
+				{
+					/* a weight transform is waiting: offer it to this launch; if the launch cannot carry it, it runs on its own */
+					const DeferredWeightTransform d = ctx.deferred_weights;
+					ctx.deferred_weights.valid = false;
+					noteDeferred(-1);
+					bk::WeightRide ride = { d.wPtr, d.uPtr, d.w.dims[0], d.w.dims[3], d.transform_size, d.conv.mode == AVOCADO_CROSS_CORRELATION_MODE, d.w.dtype,
+							d.u.dtype };
+					bool taken = false;
+					const avStatus_t status = bk::winograd_input_transform(ctx, conv, transformSize, getTensor(wDesc), getTensor(xDesc), getPointer(xMem),
+							getTensor(matricesDesc), getPointer(matricesMem), nullptr, &ride, &taken);
+					if (not taken)
+					{
+						const avStatus_t weights = bk::winograd_weight_transform(ctx, d.conv, d.transform_size, d.w, d.wPtr, d.u, d.uPtr);
+						if (weights != AVOCADO_STATUS_SUCCESS)
+							return weights;
+					}
+					return status;
+				}
 				return bk::winograd_input_transform(ctx, conv, transformSize, getTensor(wDesc), getTensor(xDesc), getPointer(xMem), getTensor(matricesDesc), getPointer(matricesMem));
 			AVOCADO_API_END
 		}

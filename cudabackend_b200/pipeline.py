@@ -70,9 +70,9 @@ class WinogradNonFused:
         self.z = api.DeviceTensor((self.n, self.h, self.w, self.k), self.dtype, self.x.mem.device)
         return self.z.upload(self.ctx, values)
 
-    def enable_fusion(self, enabled=True):
-        """Switches the context's Winograd fusion: the contraction and the output transform of forward() then run as one kernel."""
-        self.ctx.set_winograd_fusion(enabled)
+    def enable_fusion(self, flags=True):
+        """Switches the context's Winograd fusion (api.FUSE_WEIGHTS, api.FUSE_OUTPUT, both with True, none with False / 0)."""
+        self.ctx.set_winograd_fusion(flags)
 
     # ---- individual stages --------------------------------------------------------------------------------
     def weight_transform(self, rotated=False, ctx=None):

@@ -52,17 +52,26 @@ DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTest(avContextDescriptor_t context, 
  * entry point has been made on the device.  No counterpart in the reference. */
 DLL_PUBLIC avStatus_t cudaRunBoundedWaitSelfTestNoAlloc(avContextDescriptor_t context, int limitMicroseconds);
 
-/* Switches fusion of the non-fused F(4x4,3x3) Winograd pipeline on (enabled != 0) or off for one context.  The call
- * sequence of the reference stays as it is (ref app/CudaBackend.cu:401-420: weight transform, input transform,
- * cudaGemmBatched, cudaWinogradOutputTransform).  With fusion on, a cudaGemmBatched call that is the contraction of such a
- * pipeline (36 planes, (N, T), float16 / bfloat16, alpha 1, beta 0) is held back; if the next call on the context is the
- * cudaWinogradOutputTransform of exactly the tensor it was to write, ONE kernel contracts and transforms and the
- * transform-domain products are NEVER WRITTEN to the caller's workspace -- the workspace keeps whatever it held.  That
- * is the one observable difference, and the reason fusion is opt-in.  Any other call on the context (another operator, a
- * copy, a synchronisation, the end of a capture, destruction of the context or of any memory descriptor) launches the
- * held-back GEMM first, so nothing else can tell that it was deferred.  Default contexts cannot fuse.  No counterpart in
- * the reference, whose two calls always run as two kernels (src/gemm.cpp:126-209, src/winograd_nonfused.cu:703-777). */
-DLL_PUBLIC avStatus_t cudaContextSetWinogradFusion(avContextDescriptor_t context, int enabled);
+/* Switches fusion inside the non-fused Winograd pipeline on or off for one context; `flags` is 0 or a combination of the
+ * two values below.  The call sequence of the reference stays as it is (ref app/CudaBackend.cu:401-420: weight transform,
+ * input transform, cudaGemmBatched, cudaWinogradOutputTransform); what changes is how many kernels it becomes.
+ *
+ * AVOCADO_WINOGRAD_FUSE_WEIGHTS: a cudaWinogradWeightTransform of a 3x3 kernel is held back and rides along in the launch
+ *   of the cudaWinogradInputTransform that follows it (a few blocks at the front of that grid).  Its result is written as
+ *   usual, bit for bit; only the separate launch, a few microseconds of latency for 74 KB of weights, disappears.
+ * AVOCADO_WINOGRAD_FUSE_OUTPUT: a cudaGemmBatched call that is the contraction of an F(4x4,3x3) pipeline (36 planes, (N, T),
+ *   float16 / bfloat16, alpha 1, beta 0) is held back; if the next call on the context is the cudaWinogradOutputTransform
+ *   of exactly the tensor it was to write, ONE kernel contracts and transforms and the transform-domain products are
+ *   NEVER WRITTEN to the caller's workspace -- the workspace keeps whatever it held.  That is the one observable
+ *   difference, and the reason fusion is opt-in.
+ *
+ * Any other call on the context (another operator, a copy, a synchronisation, the end of a capture, destruction of the
+ * context or of any memory descriptor) launches what was held back first, in the order it was asked for, so nothing
+ * else can tell that it was deferred.  Default contexts cannot fuse.  No counterpart in the reference, whose calls always
+ * run as one kernel each (src/winograd_nonfused.cu:608-651, src/gemm.cpp:126-209, src/winograd_nonfused.cu:703-777). */
+#define AVOCADO_WINOGRAD_FUSE_WEIGHTS 1
+#define AVOCADO_WINOGRAD_FUSE_OUTPUT 2
+DLL_PUBLIC avStatus_t cudaContextSetWinogradFusion(avContextDescriptor_t context, int flags);
 
 /* Orders two contexts on the device without blocking the host: everything enqueued on `waiting` after this call runs
  * after everything enqueued on `signalling` before it.  The reference has only cudaSynchronizeWithContext, which blocks

@@ -160,6 +160,44 @@ def test_fused_pipeline_in_a_captured_graph(ctx):
     assert err["elem"] <= 8e-2 and err["rms"] <= 8e-3, err
 
 
+def test_weight_transform_rides_with_the_input_transform(ctx):
+    """FUSE_WEIGHTS: U and V are what the separate launches give, bit for bit, whichever launch computed U; a weight
+    transform that is not followed by an input transform still happens"""
+    for dtype, mdtype, ts, shape, k in (("float16", None, 4, (2, 9, 11, 40), 24), ("bfloat16", "float16", 2, (3, 14, 14, 64), 32),
+                                        ("float32", None, 4, (2, 12, 12, 32), 16), ("float16", "float32", 4, (1, 8, 8, 16), 8)):
+        n, h, w, c = shape
+        p = pipeline.WinogradNonFused(ctx, n, h, w, c, k, dtype, mdtype, ts, 3)
+        p.x.upload(ctx, common.uniform("x", p.x.shape))
+        p.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+        for rotated in (False, True):
+            p.weight_transform(rotated=rotated)
+            p.input_transform()
+            u_ref, v_ref = p.u.download_raw(ctx), p.v.download_raw(ctx)
+            p.u.mem.zero(ctx)
+            p.v.mem.zero(ctx)
+            p.enable_fusion(api.FUSE_WEIGHTS)
+            p.weight_transform(rotated=rotated)
+            p.input_transform()
+            assert np.array_equal(p.u.download_raw(ctx), u_ref) and np.array_equal(p.v.download_raw(ctx), v_ref), (dtype, mdtype, ts, rotated)
+            p.u.mem.zero(ctx)
+            p.weight_transform(rotated=rotated)  # held back ...
+            assert np.array_equal(p.u.download_raw(ctx), u_ref)  # ... until the copy to the host asks for it
+            p.enable_fusion(0)
+    # a 5x5 kernel and float64 are outside the ride: nothing is held back, results unchanged
+    p = pipeline.WinogradNonFused(ctx, 1, 6, 5, 6, 4, "float64", None, 2, 5)
+    w64 = p.wt.upload(ctx, common.he_normal_weights(4, 5, 6))
+    p.enable_fusion(api.FUSE_WEIGHTS)
+    p.weight_transform()
+    p.enable_fusion(0)
+    assert np.abs(p.u.download(ctx) - o.winograd_weight_transform(w64, 2)).max() <= 1e-12
+
+
+def test_fusion_flags_are_validated(ctx):
+    assert api.call_status("cudaContextSetWinogradFusion", ctx.handle, 4) == api.STATUS["BAD_PARAM"]
+    assert api.call_status("cudaContextSetWinogradFusion", ctx.handle, 3) == api.STATUS["SUCCESS"]
+    assert api.call_status("cudaContextSetWinogradFusion", ctx.handle, 0) == api.STATUS["SUCCESS"]
+
+
 def test_default_context_cannot_fuse(library, device_count):
     if device_count == 0:
         pytest.skip("no CUDA device visible")
