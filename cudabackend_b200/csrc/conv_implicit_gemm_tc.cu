@@ -950,8 +950,16 @@ namespace
 	{
 		const int elem = static_cast<int>(sizeof(T));
 		const int block_channels = kBlockKBytes / elem;
-		/* shapes the kernel covers; everything else goes to the direct kernel */
-		if (args.channels % block_channels != 0)
+		/* Shapes the kernel covers; everything else goes to the direct kernel.  The channel count need not fill whole
+		 * 128-byte blocks: the im2col copy fills the channels past the end of a pixel with zeros, and whatever the filter
+		 * copy fetches for those columns (the first channels of the next tap, or zeros past the end of the row) is
+		 * multiplied by them.  What TMA needs is 16-byte row pitches: C and kh*kw*C times the element size. */
+		const int taps_all = args.kernel_h * args.kernel_w;
+		if ((args.channels * elem) % 16 != 0 or (static_cast<long long>(taps_all) * args.channels * elem) % 16 != 0)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		/* with floating-point filters a non-finite value in the next tap would turn that zero product into NaN: keep
+		 * partial blocks for the integer case, where it cannot happen, and for float filters only when blocks are whole */
+		if (not Element<T>::kInteger and args.channels % block_channels != 0)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		const int out_align = Element<T>::kInteger ? 16 : 8;
 		if (args.filters % out_align != 0 or args.filters < 16)
@@ -969,9 +977,8 @@ namespace
 		for (int i = 0; i < 2; i++)
 			if (lower[i] < -128 or lower[i] > 127 or upper[i] < -128 or upper[i] > 127)
 				return AVOCADO_STATUS_NOT_SUPPORTED;
-		/* im2col maps of tensors below 128 KB are avoided: small problems do not need this kernel */
-		const long long x_bytes = static_cast<long long>(args.batch) * args.height * args.width * args.channels * elem;
-		if (x_bytes < 131072)
+		/* less than one block of output pixels: the direct kernel is the better fit */
+		if (pixels < kBlockM)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		if (reinterpret_cast<uintptr_t>(args.x) % 16 != 0 or reinterpret_cast<uintptr_t>(args.w) % 16 != 0 or reinterpret_cast<uintptr_t>(args.y) % 16 != 0
 				or (args.z != nullptr and reinterpret_cast<uintptr_t>(args.z) % 16 != 0))
@@ -1011,7 +1018,7 @@ namespace
 		p.kernel_w = args.kernel_w;
 		p.rotate = args.rotate_kernel ? 1 : 0;
 		p.m_blocks = static_cast<int>((pixels + kBlockM - 1) / kBlockM);
-		p.c_blocks = args.channels / block_channels;
+		p.c_blocks = (args.channels + block_channels - 1) / block_channels;
 		p.k_blocks = taps * p.c_blocks;
 		p.bias = args.bias;
 		p.scales = reinterpret_cast<const float*>(args.scales);

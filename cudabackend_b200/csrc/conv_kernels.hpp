@@ -38,6 +38,15 @@ namespace bk
 			const void *vPtr, const avocado::backend::b200::TensorObject &u, const void *uPtr, const avocado::backend::b200::TensorObject &y, void *yPtr,
 			const void *biasPtr, const void *zPtr, const void *alpha1, const void *alpha2, const void *beta,
 			avocado::backend::avActivationType_t activation, int *deviceStatus);
+
+	/* float32 convolution by explicit lowering onto the 3xTF32 tensor-core GEMM (conv_lowered.cu) */
+	avocado::backend::avStatus_t launch_conv_lowered_tf32(avocado::backend::b200::ContextObject &ctx, const ConvArgs &args, const void *alpha1,
+			const void *alpha2, const void *beta);
+
+	/* rows[N*Ho*Wo, kh*kw*pixelBytes] of the explicit lowering for raw device pointers (im2row.cu); pixelBytes = C * element size,
+	 * zero padding value */
+	avocado::backend::avStatus_t im2row_words(avocado::backend::b200::ContextObject &ctx, const void *input, void *rows, int batch, int height, int width,
+			int outHeight, int outWidth, int kernelH, int kernelW, int padH, int padW, bool rotate, long long pixelBytes);
 } /* namespace bk */
 
 #endif /* B200_CONV_KERNELS_HPP_ */

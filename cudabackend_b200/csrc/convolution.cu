@@ -146,6 +146,17 @@ namespace
 		return checkForErrors();
 	}
 
+	/* AVOCADO_B200_CONV=direct keeps every convolution on the CUDA-core kernel (A/B comparison) */
+	bool lowering_enabled()
+	{
+		static const bool enabled = []()
+		{
+			const char *env = std::getenv("AVOCADO_B200_CONV");
+			return not (env != nullptr and std::strcmp(env, "direct") == 0);
+		}();
+		return enabled;
+	}
+
 	enum class Algorithm
 	{
 		ImplicitGemm, WinogradFused
@@ -240,6 +251,13 @@ namespace
 				status = launch_winograd_fused_tc(ctx, args, x.dtype, y.dtype, alpha1, alpha2, beta);
 			if (status != AVOCADO_STATUS_NOT_SUPPORTED)
 				return status;
+			/* float32 has no implicit tensor-core kernel: lowering + 3xTF32 GEMM, before the CUDA-core kernel of last resort */
+			if (algorithm == Algorithm::ImplicitGemm and x.dtype == AVOCADO_DTYPE_FLOAT32 and lowering_enabled())
+			{
+				status = launch_conv_lowered_tf32(ctx, args, alpha1, alpha2, beta);
+				if (status != AVOCADO_STATUS_NOT_SUPPORTED)
+					return status;
+			}
 			return launch_direct(ctx, args, x.dtype, y.dtype, alpha1, alpha2, beta);
 		AVOCADO_API_END
 	}

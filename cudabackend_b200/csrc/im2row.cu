@@ -23,6 +23,8 @@
 #include "objects.hpp"
 #include "device_utils.cuh"
 
+#include "conv_kernels.hpp"
+
 #include <algorithm>
 #include <cstring>
 
@@ -100,6 +102,30 @@ namespace
 		return checkForErrors();
 	}
 }
+
+namespace bk
+{
+	avStatus_t im2row_words(ContextObject &ctx, const void *input, void *rows, int batch, int height, int width, int outHeight, int outWidth, int kernelH,
+			int kernelW, int padH, int padW, bool rotate, long long pixelBytes)
+	{
+		Im2RowShape s;
+		s.batch = batch;
+		s.height = height;
+		s.width = width;
+		s.out_height = outHeight;
+		s.out_width = outWidth;
+		s.kernel_h = kernelH;
+		s.kernel_w = kernelW;
+		s.pad_h = padH;
+		s.pad_w = padW;
+		s.rotate = rotate ? 1 : 0;
+		const uint8_t zero_padding[16] = { };
+		if (pixelBytes % 16 != 0 or pixelBytes > 0x7FFFFFFFll or reinterpret_cast<uintptr_t>(input) % 16 != 0 or reinterpret_cast<uintptr_t>(rows) % 16 != 0)
+			return AVOCADO_STATUS_NOT_SUPPORTED;
+		ctx.setDevice();
+		return launch<uint4>(ctx, input, rows, s, static_cast<int>(pixelBytes / 16), zero_padding, 4);
+	}
+} /* namespace bk */
 
 namespace avocado
 {

@@ -239,3 +239,53 @@ def test_int8_short_and_general_epilogue_agree(ctx):
             assert np.max(np.abs(got.astype(np.int32) - ref.astype(np.int32))) <= 1
         else:
             assert np.array_equal(got, ref), (alpha1, activation)
+
+
+@pytest.mark.parametrize("shape", [(2, 14, 14, 64, 64), (2, 7, 9, 48, 16), (4, 12, 12, 16, 32), (1, 16, 8, 144, 80)])
+def test_int8_tensor_core_small_and_partial_channel_blocks(ctx, shape):
+    """small layers and channel counts that do not fill the kernel's 128-byte channel blocks (C = 64, 48, 16, 144) also run
+    on the tensor-core kernel: the missing channels of a block arrive as zeros.  Bit exact like every int8 case."""
+    n, h, w, c, k = shape
+    got, ref = int8_case(ctx, n, h, w, c, k, (5e-5, 2e-4), activation="relu", with_z=True)
+    assert np.array_equal(got, ref)
+    got, ref = int8_case(ctx, n, h, w, c, k, None, int32_output=True)
+    assert np.array_equal(got, ref)
+    got, ref = int8_case(ctx, n, h, w, c, k, (5e-5, 2e-4), rotated=True)
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("shape", [(4, 28, 28, 64, 64), (2, 9, 10, 24, 16), (3, 14, 15, 128, 72), (2, 8, 8, 16, 8)])
+def test_implicit_gemm_float32_on_tensor_cores(ctx, shape):
+    """float32 through cudaConvolutionImplicitGemmForward: lowered (im2row) onto the 3xTF32 tcgen05 GEMM, with the whole
+    epilogue formula and with none; float32-level accuracy (1e-3 is the stated bound, the 3xTF32 scheme is well inside)"""
+    n, h, w, c, k = shape
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "float32")
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+    d.implicit_gemm()
+    assert o.error_metrics(d.y.download(ctx), o.conv2d_forward(x, wt))["elem"] <= 1e-4
+    b = d.set_bias(common.uniform("b", (k,), -0.1, 0.1))
+    z = d.set_z(common.uniform("z", d.y.shape))
+    y0 = d.y.upload(ctx, common.uniform("y", d.y.shape))
+    d.implicit_gemm(alpha1=1.1, alpha2=1.2, beta=0.1, activation="tanh")
+    f = lambda v: float(np.float32(v))
+    ref = o.conv2d_forward(x, wt, bias=b, z=z, y=y0, alpha1=f(1.1), alpha2=f(1.2), beta=f(0.1), activation="tanh")
+    assert o.error_metrics(d.y.download(ctx), ref)["elem"] <= 1e-4
+
+
+def test_implicit_gemm_float32_rotated_5x5_and_chunked(ctx):
+    """CROSS_CORRELATION_MODE, a 5x5 kernel, and a batch large enough that the row matrix is built in several chunks"""
+    n, h, w, c, k = 2, 12, 11, 16, 16
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "float32", kernel_size=5)
+    d.conv = api.ConvolutionDescriptor(api.CROSS_CORRELATION_MODE, (-2, -2))
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 5, c))
+    d.implicit_gemm(activation="relu")
+    ref = o.conv2d_forward(x, wt, padding=(-2, -2), mode=1, activation="relu")
+    assert o.error_metrics(d.y.download(ctx), ref)["elem"] <= 1e-4
+    n, h, w, c, k = 24, 56, 56, 64, 32  # 24 * 3136 * 576 * 4 bytes = 1.7 GB of rows: two chunks
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, "float32")
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+    d.implicit_gemm()
+    assert o.error_metrics(d.y.download(ctx), o.conv2d_forward(x, wt))["elem"] <= 1e-4
