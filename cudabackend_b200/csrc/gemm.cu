@@ -497,6 +497,23 @@ namespace
 		return value;
 	}
 
+	/* out[b][c][r] = in[b][r][c] for a small row-major 16-bit tensor (the transformed filters of a dX pass) */
+	__global__ void kernel_transpose_batched_16(uint16_t *__restrict__ out, const uint16_t *__restrict__ in, int rows, int cols)
+	{
+		__shared__ uint16_t tile[32][34];
+		const int b = blockIdx.z;
+		const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+		const uint16_t *src = in + static_cast<size_t>(b) * rows * cols;
+		uint16_t *dst = out + static_cast<size_t>(b) * rows * cols;
+		for (int i = threadIdx.y; i < 32; i += blockDim.y)
+			if (r0 + i < rows and c0 + static_cast<int>(threadIdx.x) < cols)
+				tile[i][threadIdx.x] = src[static_cast<size_t>(r0 + i) * cols + c0 + threadIdx.x];
+		__syncthreads();
+		for (int i = threadIdx.y; i < 32; i += blockDim.y)
+			if (c0 + i < cols and r0 + static_cast<int>(threadIdx.x) < rows)
+				dst[static_cast<size_t>(c0 + i) * rows + r0 + threadIdx.x] = tile[threadIdx.x][i];
+	}
+
 	bool tc_eligible(const ContextObject &ctx, const GemmShape &s, avDataType_t dtype, const void *A, const void *B, const void *C, float beta)
 	{
 		if (dtype != AVOCADO_DTYPE_FLOAT16 and dtype != AVOCADO_DTYPE_BFLOAT16)
@@ -584,10 +601,29 @@ namespace
 				const float a = getAlphaValue<float>(alpha);
 				const float b = getBetaValue<float>(beta);
 				const bool eligible = tc_eligible(ctx, s, cType, A, B, C, b);
-				if (forced_path() == 2 and not eligible)
-					return AVOCADO_STATUS_NOT_SUPPORTED;
 				if (eligible and forced_path() != 1)
 					return launch_tc(ctx, s, cType, A, B, C, a, ctx.getDeviceStatus());
+				/* op(B) = B, stored [Kc, N] (the dX contraction: tiles x filters times filters x channels): B is the small
+				 * operand there, so it is transposed into scratch and the same tensor-core kernel runs on it */
+				if (not s.transA and not s.transB and forced_path() != 1 and s.ldb == s.N and s.batch <= 65535 and s.N % 8 == 0)
+				{
+					GemmShape t = s;
+					t.transB = true;
+					t.ldb = s.Kc;
+					t.strideB = static_cast<long long>(s.Kc) * s.N;
+					const size_t b_bytes = static_cast<size_t>(s.batch) * s.Kc * s.N * 2;
+					/* C stands in for the scratch pointer in the test: both are at least 16-byte aligned */
+					if (b_bytes <= (64u << 20) and tc_eligible(ctx, t, cType, A, C, C, b))
+					{
+						uint16_t *transposed = reinterpret_cast<uint16_t*>(ctx.getWorkspace(b_bytes));
+						const dim3 block(32, 8);
+						const dim3 grid((s.N + 31) / 32, (s.Kc + 31) / 32, s.batch);
+						kernel_transpose_batched_16<<<grid, block, 0, stream>>>(transposed, reinterpret_cast<const uint16_t*>(B), s.Kc, s.N);
+						return launch_tc(ctx, t, cType, A, transposed, C, a, ctx.getDeviceStatus());
+					}
+				}
+				if (forced_path() == 2)
+					return AVOCADO_STATUS_NOT_SUPPORTED;
 				if (cType == AVOCADO_DTYPE_FLOAT16)
 					return launch_simt<half, float, half>(stream, s, A, B, C, a, b);
 				return launch_simt<__nv_bfloat16, float, __nv_bfloat16>(stream, s, A, B, C, a, b);

@@ -89,6 +89,20 @@ def test_gemm_batched_tensor_core(ctx, dtype, shape):
     assert o.error_metrics(got, ref)["elem"] <= {"float16": 1e-3, "bfloat16": 8e-3}[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_gemm_batched_tensor_core_16bit_nn(ctx, dtype, shape):
+    """op(B) = B (the dX contraction of a 16-bit layer): B is transposed into scratch and the tensor-core kernel runs"""
+    batch, m, n, k = shape
+    r = np.random.default_rng(17)
+    a = r.uniform(-1, 1, (batch, m, k))
+    b = r.normal(0, np.sqrt(2.0 / k), (batch, k, n))
+    c0 = np.full((batch, m, n), 7.0)
+    got, a64, b64, _ = run_gemm(ctx, "cudaGemmBatched", a, b, c0, dtype, False, False, 0.75, None)
+    ref = o.gemm_batched(a64, b64, False, False, alpha=0.75)
+    assert o.error_metrics(got, ref)["elem"] <= {"float16": 1e-3, "bfloat16": 8e-3}[dtype]
+
+
 def test_gemm_batched_tensor_core_alpha_and_determinism(ctx):
     batch, m, n, k = 36, 392, 64, 64
     r = np.random.default_rng(15)
