@@ -591,6 +591,14 @@ namespace
 				const int b = static_cast<int>(getBetaValue<float>(beta));
 				if ((a != 0 and a != 1) or (b != 0 and b != 1))
 					return AVOCADO_STATUS_BAD_PARAM;
+				if (a == 1 and b == 0 and forced_path() != 1)
+				{
+					const avStatus_t status = bk::launch_gemm_i8(ctx, s, A, B, C);
+					if (status != AVOCADO_STATUS_NOT_SUPPORTED)
+						return status;
+				}
+				if (forced_path() == 2)
+					return AVOCADO_STATUS_NOT_SUPPORTED;
 				return launch_simt<int8_t, int32_t, int32_t>(stream, s, A, B, C, a, b);
 			}
 			case AVOCADO_DTYPE_FLOAT16:

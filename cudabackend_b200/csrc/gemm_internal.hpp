@@ -22,6 +22,10 @@ namespace bk
 	 * NOT_SUPPORTED, launching nothing, for shapes it does not cover. */
 	avocado::backend::avStatus_t launch_gemm_tf32(avocado::backend::b200::ContextObject &ctx, const GemmShape &s, const void *A, const void *B, void *C,
 			float alpha, float beta);
+
+	/* int8 x int8^T -> int32 on the tensor cores (one matrix, op(A) = A, op(B) = B^T).  Returns NOT_SUPPORTED, launching
+	 * nothing, for shapes it does not cover. */
+	avocado::backend::avStatus_t launch_gemm_i8(avocado::backend::b200::ContextObject &ctx, const GemmShape &s, const void *A, const void *B, void *C);
 } /* namespace bk */
 
 #endif /* B200_GEMM_INTERNAL_HPP_ */

@@ -149,6 +149,11 @@ namespace umma
 		asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
 				::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smemSrc)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 	}
+	__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *smemSrc, int c0, int c1)
+	{
+		asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+				::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smemSrc)), "r"(c0), "r"(c1) : "memory");
+	}
 	__device__ __forceinline__ void tma_store_commit()
 	{
 		asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -70,6 +70,22 @@ def test_gemm_int8(ctx):
     assert np.array_equal(got.astype(np.int64), a.astype(np.int64) @ b.astype(np.int64).T)
 
 
+@pytest.mark.parametrize("shape", [(300, 64, 576), (1000, 128, 1152), (129, 72, 2304), (77, 200, 144), (4000, 256, 64), (128, 16, 16)])
+def test_gemm_int8_tensor_core(ctx, shape):
+    """the int8 product at the sizes of a lowered convolution (rows of im2row times filters): tcgen05 kind::i8, exact;
+    row counts that are not multiples of 128, filter counts between the column blocks, several tiles per CTA"""
+    m, n, k = shape
+    r = np.random.default_rng(18)
+    a = r.integers(-127, 128, (m, k), dtype=np.int8)
+    b = r.integers(-127, 128, (n, k), dtype=np.int8)
+    c0 = np.full((m, n), 7, dtype=np.int32)  # must be overwritten everywhere
+    got, _, _, _ = run_gemm(ctx, "cudaGemm", a, b, c0, "int8", False, True, None, None, out_dtype="int32")
+    assert np.array_equal(got.astype(np.int64), a.astype(np.int64) @ b.astype(np.int64).T)
+    # beta = 1 accumulates onto C (CUDA-core kernel): same exact arithmetic
+    got, _, _, _ = run_gemm(ctx, "cudaGemm", a, b, c0, "int8", False, True, None, 1.0, out_dtype="int32")
+    assert np.array_equal(got.astype(np.int64), a.astype(np.int64) @ b.astype(np.int64).T + 7)
+
+
 # (batch, rows of A, rows of B, contraction): Winograd-shaped products for the tensor-core kernel; the odd row
 # counts exercise the clipped last tile, 200/72 the partial contraction block and the N tail.
 TC_SHAPES = [(36, 128, 64, 64), (36, 392, 64, 64), (16, 1000, 128, 128), (36, 130, 32, 64), (4, 77, 72, 200), (3, 300, 256, 64), (2, 129, 320, 96)]
