@@ -38,10 +38,10 @@ namespace
 	constexpr int kBlockTiles = 128;
 	constexpr int kBlockFilters = 64;
 	constexpr int kBlockChannels = 64; /* 128 bytes of float16 */
-	/* A stage holds the operands of all four planes of a group for one block of 64 channels, so that consecutive MMAs go
-	 * to different accumulators: an MMA that accumulates into the tile the previous one wrote waits for it (about 200
-	 * cycles), and the four MMAs of one plane issued in a row set the pace of the whole kernel (about 700 cycles per
-	 * 24 KB of operands, measured).  Interleaved, a plane's accumulator is touched again only three MMAs later. */
+	/* A stage holds the operands of all four planes of a group for one block of 64 channels, and the MMAs of a stage are
+	 * issued contraction step outermost, plane innermost: consecutive MMAs go to different accumulators, and the producer
+	 * moves 96 KB per barrier round trip instead of 24 KB.  Measured on the 128 x 28 x 28 x 128 layer: 54 us with one plane
+	 * per stage (eight stages of 24 KB), 46 us with this form (two stages of 96 KB). */
 	constexpr int kStagePlanes = 4;
 	constexpr int kStages = 2;
 	constexpr int kABytes = kBlockTiles * 128;
