@@ -850,6 +850,16 @@ def sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_pe
     return record
 
 
+def headline_steps_per_graph(args):
+    """Steps replayed by one graph launch: consecutive steps run on consecutive buffer sets, so a graph of `rotation` steps is
+    the same work as `rotation` single-step graphs without the gap between graph launches."""
+    if args.no_graph:
+        return 1
+    if args.steps_per_graph in (1, args.rotation):
+        return args.steps_per_graph
+    return args.rotation if args.steps % args.rotation == 0 else 1
+
+
 def launch_mode(args, steps_per_graph=1):
     if args.no_graph:
         return "kernel by kernel"
@@ -985,7 +995,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     # ---- headline: the configured workload, every rank its own batch ---------------------------------------
     matrices_dtype = args.matrices or cfg["dtype"]
     m = Measurement(args, args.config, cfg, matrices_dtype, rank, world, local_rank, seed_offset=rank, fusion=FUSION[args.fusion])
-    m.capture(1)
+    spg = headline_steps_per_graph(args)
+    m.capture(spg)
     elapsed_ms, done, clocks, wall_ms = m.timed(args.steps, args.warmup, sampler if rank == 0 else None)
     ms_per_step = elapsed_ms / done
     stage_ms = m.stage_times(max(20, min(args.steps, 200)))
@@ -1000,7 +1011,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         m.sync_all()
         parity = m.parity()
     m.barrier()
-    m.capture(1)
+    m.capture(spg)
     sustained = m.sustained(args.sustained_seconds, sampler if rank == 0 else None) if not args.only_headline else None
     m.destroy_graphs()
     e2e = m.e2e(args.steps, args.warmup)
@@ -1029,7 +1040,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
                            "parallelism": "batch sharded, dp%d: every rank runs the configuration's batch (weak scaling); the split of the "
                                           "configuration's own batch over the ranks is under `sharded`" % world},
                 "images_per_s": cfg["n"] * world / (ms_per_step * 1e-3), "host_wall_ms_per_step": wall_ms / done,
-                "e2e": e2e, "gpu_launches": launches, "launch_mode": launch_mode(args), "stage_ms": stage_ms, "clocks": clocks}
+                "e2e": e2e, "gpu_launches": launches, "launch_mode": launch_mode(args, spg), "stage_ms": stage_ms, "clocks": clocks}
         roof = roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference)
         line["roofline"] = roof
         if "stage_gbs" in roof:
@@ -1056,7 +1067,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
             # parity and the sustained replay are single-GPU properties, measured at N = 1; at N > 1 the sub-records are the
             # weak-scaling throughput of each configuration
             record = sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_peaks, sampler, want_parity=(world == 1),
-                                want_sustained=(world == 1))
+                                want_sustained=(world == 1), steps_per_graph=spg)
             if rank == 0:
                 configs[key] = record
         if rank == 0:
@@ -1117,6 +1128,9 @@ def main():
                              "weights (the weight transform rides in the input transform's launch), output (contraction + output transform as one "
                              "kernel, M not written), all")
     parser.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a captured graph")
+    parser.add_argument("--steps-per-graph", type=int, default=0,
+                        help="consecutive steps (one per rotating buffer set) replayed by one graph launch: 1, or the rotation; 0 = the rotation "
+                             "when it divides --steps, else 1")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -10,8 +10,10 @@
  *                 consecutive output pixels' input vectors (128 bytes each) straight from the NHWC tensor into
  *                 128-byte-swizzled shared memory; pixels that fall outside the image arrive as zeros (= padding)
  *   B operand     the filters [K, kh*kw*C], already contiguous along the contraction: tiled TMA copy
- *   MMA           tcgen05.mma cta_group::1, M = 128, N = 64/128/256; kind::i8 with int32 accumulation for int8,
- *                 kind::f16 with float32 accumulation for float16 / bfloat16; accumulator double-buffered in TMEM
+ *   MMA           tcgen05.mma, N = 64/128/256; kind::i8 with int32 accumulation for int8, kind::f16 with float32
+ *                 accumulation for float16 / bfloat16; accumulator double-buffered in TMEM.  Layers of at least 256
+ *                 output pixels run on CTA pairs (cta_group::2, M = 256, each CTA holding half of the filter block),
+ *                 smaller ones on single CTAs (cta_group::1, M = 128)
  *   epilogue      four warps drain TMEM: + bias, (requantisation | alpha/z/activation/beta), 16-byte stores
  *
  * Roofline: with C = K = 256 the contraction is 2*9*C*K = 1.18 MFLOP per output pixel against 512 bytes moved, so
@@ -413,6 +415,10 @@ namespace
 		const uint32_t tmem_base = tmem_base_slot;
 		volatile int *abort_ptr = &abort_flag;
 		const int taps = p.kernel_h * p.kernel_w;
+		/* everything above touched only shared memory, barriers and TMEM: the kernel after this one on the stream may
+		 * start its own set-up now, and this one waits here for the kernel before it */
+		chain_release();
+		chain_wait();
 
 		if (warp == 0)
 		{
@@ -602,11 +608,20 @@ namespace
 	}
 
 	/*
-	 * The same convolution on CTA pairs (opt-in, see pair_kernel_enabled).  With 256 filters per tile the single-CTA
-	 * kernel copies a 32 KB filter block into shared memory for every 128 pixels.  Here two CTAs on neighbouring SMs
-	 * share one 256 pixel x 256 filter tile: each loads its own 128 pixels and only HALF of the filter block, and the
-	 * first CTA of the pair issues tcgen05.mma cta_group::2 (M = 256), which reads both halves in place and leaves each
-	 * CTA with the accumulator rows of its own pixels.  Shared-memory fill per output drops by a third.
+	 * The same convolution on CTA pairs: two CTAs on neighbouring SMs share one tile of 256 pixels x BLOCK_N filters.  Each
+	 * loads its own 128 pixels and only HALF of the filter block; the first CTA of the pair issues tcgen05.mma
+	 * cta_group::2 (M = 256), which reads both halves in place and leaves each CTA with the accumulator rows of its own
+	 * pixels.
+	 *
+	 * Why this is the default form.  Measured on this kernel's loads and MMAs without an epilogue (148 CTAs, int8, 256
+	 * filters): the thread that issues the MMAs spends about 100 cycles in a wait on a full barrier, 55 per MMA and 120 in
+	 * a commit, and the thread that issues the copies about 370 per 128-byte contraction block; a shared-memory stage
+	 * stays occupied for the 1500-1900 cycles its copies take to land plus the time its MMAs run.  With one 128-byte
+	 * block per stage the single-CTA kernel is therefore paced by those two threads and by the four stages that fit
+	 * (600 cycles per block and 128 pixels, 870 with the epilogue warps running) and not by the tensor pipe (4 MMAs of
+	 * 139 cycles).  A pair halves the filter bytes per SM, so a stage can hold KB = 2 blocks three or four deep: one wait
+	 * and one commit per eight MMAs, half as many copies per SM and pixel, and the pipe sets the pace (560 cycles per
+	 * block and 256 pixels).
 	 *
 	 *   full_bar[s]        first CTA only: one arrival (its producer, which also posts the bytes of BOTH CTAs' copies);
 	 *                      the second CTA's copies report their bytes to it
@@ -614,24 +629,24 @@ namespace
 	 *   tmem_full_bar[a]   both CTAs: the commit after a tile's last MMA arrives on both
 	 *   tmem_empty_bar[a]  first CTA only: one arrival per epilogue warp of both CTAs
 	 */
-	constexpr int kPairBlockN = 256;
-	constexpr int kPairHalfN = kPairBlockN / 2;
-
-	template<int STAGES>
+	template<int BLOCK_N, int KB, int STAGES>
 	struct IgPairConfig
 	{
+			static constexpr int kHalfN = BLOCK_N / 2;
 			static constexpr int kABytes = kBlockM * kBlockKBytes;
-			static constexpr int kBBytes = kPairHalfN * kBlockKBytes;
-			static constexpr int kStageBytes = kABytes + kBBytes;
+			static constexpr int kBBytes = kHalfN * kBlockKBytes;
+			static constexpr int kBlockBytes = kABytes + kBBytes; /* one 128-byte contraction block of both operands */
+			static constexpr int kStageBytes = KB * kBlockBytes;
 			static constexpr int kSmemBytes = STAGES * kStageBytes + 1024;
-			static constexpr int kTmemColumns = 2 * kPairBlockN;
+			static constexpr int kTmemColumns = 2 * BLOCK_N;
+			static_assert(kSmemBytes <= 232448, "stages exceed the shared memory of an SM");
 	};
 
-	template<typename T, int STAGES>
+	template<typename T, int BLOCK_N, int KB, int STAGES>
 	__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) kernel_implicit_gemm_tc_pair(const __grid_constant__ CUtensorMap mapX,
 			const __grid_constant__ CUtensorMap mapW, IgParams p, int *deviceStatus)
 	{
-		using Cfg = IgPairConfig<STAGES>;
+		using Cfg = IgPairConfig<BLOCK_N, KB, STAGES>;
 		constexpr int kElemsPerBlock = kBlockKBytes / static_cast<int>(sizeof(T));
 		constexpr int kMmaK = 32 / static_cast<int>(sizeof(T));
 		extern __shared__ uint8_t smem_raw[];
@@ -644,8 +659,8 @@ namespace
 		__shared__ uint32_t tmem_base_slot;
 		__shared__ int abort_flag;
 		__shared__ volatile int epilogue_go;
-		__shared__ __align__(16) float scale_s[kPairBlockN];
-		__shared__ __align__(16) float bias_s[kPairBlockN];
+		__shared__ __align__(16) float scale_s[BLOCK_N];
+		__shared__ __align__(16) float bias_s[BLOCK_N];
 
 		const int warp = threadIdx.x / 32;
 		const int lane = threadIdx.x % 32;
@@ -682,6 +697,10 @@ namespace
 		const uint32_t tmem_base = tmem_base_slot;
 		volatile int *abort_ptr = &abort_flag;
 		const int taps = p.kernel_h * p.kernel_w;
+		/* everything above touched only shared memory, barriers and TMEM: the kernel after this one on the stream may
+		 * start its own set-up now, and this one waits here for the kernel before it */
+		chain_release();
+		chain_wait();
 
 		if (warp == 0)
 		{
@@ -702,39 +721,45 @@ namespace
 					const int rem = m0 - n * image;
 					const int oh = rem / p.out_w;
 					const int ow = rem - oh * p.out_w;
+					const int filter0 = nb * BLOCK_N + static_cast<int>(rank) * Cfg::kHalfN;
 					int r = 0, s = 0, cb = 0, tap = 0;
-					for (int kb = 0; kb < p.k_blocks; kb++)
+					for (int kb = 0; kb < p.k_blocks; kb += KB)
 					{
-						const int wtap = p.rotate ? (taps - 1 - tap) : tap;
+						const int count = min(KB, p.k_blocks - kb);
 						if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
 						{
 							umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
 							ok = false;
 							break;
 						}
-						uint8_t *a_dst = smem + stage * Cfg::kStageBytes;
-						uint8_t *b_dst = a_dst + Cfg::kABytes;
 						const uint32_t bar = umma::map_to_cta(umma::smem_u32(&full_bar[stage]), 0);
 						if (rank == 0)
-							umma::mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
-						umma::tma_load_im2col_4d_pair(a_dst, &mapX, bar, cb * kElemsPerBlock, ow + p.pad_w, oh + p.pad_h, n, static_cast<uint16_t>(s),
-								static_cast<uint16_t>(r));
-						umma::tma_load_2d_pair(b_dst, &mapW, bar, wtap * p.channels + cb * kElemsPerBlock,
-								nb * kPairBlockN + static_cast<int>(rank) * kPairHalfN);
+							umma::mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>(2 * count * Cfg::kBlockBytes));
+#pragma unroll
+						for (int j = 0; j < KB; j++)
+							if (j < count)
+							{
+								const int wtap = p.rotate ? (taps - 1 - tap) : tap;
+								uint8_t *a_dst = smem + stage * Cfg::kStageBytes + j * Cfg::kBlockBytes;
+								uint8_t *b_dst = a_dst + Cfg::kABytes;
+								umma::tma_load_im2col_4d_pair(a_dst, &mapX, bar, cb * kElemsPerBlock, ow + p.pad_w, oh + p.pad_h, n, static_cast<uint16_t>(s),
+										static_cast<uint16_t>(r));
+								umma::tma_load_2d_pair(b_dst, &mapW, bar, wtap * p.channels + cb * kElemsPerBlock, filter0);
+								if (++cb == p.c_blocks)
+								{
+									cb = 0;
+									tap++;
+									if (++s == p.kernel_w)
+									{
+										s = 0;
+										r++;
+									}
+								}
+							}
 						if (++stage == STAGES)
 						{
 							stage = 0;
 							phase ^= 1u;
-						}
-						if (++cb == p.c_blocks)
-						{
-							cb = 0;
-							tap++;
-							if (++s == p.kernel_w)
-							{
-								s = 0;
-								r++;
-							}
 						}
 					}
 				}
@@ -745,7 +770,7 @@ namespace
 			if (lane == 0 and rank == 0)
 			{
 				constexpr uint32_t idesc = umma::make_instr_desc(Element<T>::kAccum, Element<T>::kFormat, Element<T>::kFormat, false, false, 2 * kBlockM,
-						kPairBlockN);
+						BLOCK_N);
 				const uint64_t a_desc0 = umma::make_smem_desc(umma::smem_u32(smem), 16, 1024, umma::kSwizzle128B);
 				int stage = 0;
 				uint32_t phase = 0;
@@ -761,9 +786,10 @@ namespace
 						break;
 					}
 					umma::tcgen05_fence_after();
-					const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kPairBlockN);
-					for (int kb = 0; kb < p.k_blocks; kb++)
+					const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+					for (int kb = 0; kb < p.k_blocks; kb += KB)
 					{
+						const int count = min(KB, p.k_blocks - kb);
 						if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
 						{
 							umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
@@ -771,13 +797,18 @@ namespace
 							break;
 						}
 						umma::tcgen05_fence_after();
-						const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (Cfg::kStageBytes / 16));
-						const uint64_t b_desc = a_desc + Cfg::kABytes / 16;
-						static_assert(kElemsPerBlock / kMmaK == 4, "a stage is four MMAs deep");
-						if constexpr (Element<T>::kInteger)
-							umma::mma_i8_pair_k4(tmem_d, a_desc, b_desc, idesc, kb != 0);
-						else
-							umma::mma_f16_pair_k4(tmem_d, a_desc, b_desc, idesc, kb != 0);
+						static_assert(kElemsPerBlock / kMmaK == 4, "a contraction block is four MMAs deep");
+#pragma unroll
+						for (int j = 0; j < KB; j++)
+							if (j < count)
+							{
+								const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((stage * Cfg::kStageBytes + j * Cfg::kBlockBytes) / 16);
+								const uint64_t b_desc = a_desc + Cfg::kABytes / 16;
+								if constexpr (Element<T>::kInteger)
+									umma::mma_i8_pair_k4(tmem_d, a_desc, b_desc, idesc, (kb + j) != 0);
+								else
+									umma::mma_f16_pair_k4(tmem_d, a_desc, b_desc, idesc, (kb + j) != 0);
+							}
 						umma::mma_commit_pair(&empty_bar[stage], 3);
 						if (++stage == STAGES)
 						{
@@ -806,13 +837,13 @@ namespace
 				const int mb = tile / p.n_blocks;
 				const int acc = it & 1;
 				const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
-				const int k0 = nb * kPairBlockN;
+				const int k0 = nb * BLOCK_N;
 
 				if (staged_nb != nb)
 				{
 					if (staged_nb >= 0)
 						umma::named_barrier_sync(1, kEpilogueThreads);
-					for (int j = epi_thread; j < kPairBlockN; j += kEpilogueThreads)
+					for (int j = epi_thread; j < BLOCK_N; j += kEpilogueThreads)
 					{
 						const int k = k0 + j;
 						float sc = 1.0f, bi = 0.0f;
@@ -842,9 +873,9 @@ namespace
 
 				const int m = mb * (2 * kBlockM) + static_cast<int>(rank) * kBlockM + row;
 				const bool row_valid = m < p.pixels;
-				const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kPairBlockN);
+				const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-				for (int chunk = column_half * (kPairBlockN / 64); chunk < (column_half + 1) * (kPairBlockN / 64); chunk++)
+				for (int chunk = column_half * (BLOCK_N / 64); chunk < (column_half + 1) * (BLOCK_N / 64); chunk++)
 				{
 					uint32_t r[32];
 					umma::tmem_load_32x32(t_addr + static_cast<uint32_t>(chunk * 32), r);
@@ -875,18 +906,18 @@ namespace
 		}
 	}
 
-	template<typename T, int STAGES>
+	template<typename T, int BLOCK_N, int KB, int STAGES>
 	avStatus_t launch_pair(ContextObject &ctx, const CUtensorMap &mapX, const CUtensorMap &mapW, IgParams &p)
 	{
-		using Cfg = IgPairConfig<STAGES>;
-		auto kernel = kernel_implicit_gemm_tc_pair<T, STAGES>;
+		using Cfg = IgPairConfig<BLOCK_N, KB, STAGES>;
+		auto kernel = kernel_implicit_gemm_tc_pair<T, BLOCK_N, KB, STAGES>;
 		static PerDeviceOnce configured;
 		if (configured.run(ctx.device, [&]() -> cudaError_t { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes); }) != cudaSuccess)
 		{
 			cudaGetLastError();
 			return AVOCADO_STATUS_EXECUTION_FAILED;
 		}
-		p.n_blocks = (p.filters + kPairBlockN - 1) / kPairBlockN;
+		p.n_blocks = (p.filters + BLOCK_N - 1) / BLOCK_N;
 		const int m_pairs = (p.pixels + 2 * kBlockM - 1) / (2 * kBlockM);
 		const long long tiles = static_cast<long long>(m_pairs) * p.n_blocks;
 		if (tiles > 0x7FFFFFFFll)
@@ -895,7 +926,10 @@ namespace
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
 		const int pairs = std::max(1, std::min(p.num_tiles, sms / 2));
-		kernel<<<2 * pairs, kThreads, Cfg::kSmemBytes, ctx.getStream()>>>(mapX, mapW, p, ctx.getDeviceStatus());
+		const cudaError_t launched = launch_chained(kernel, dim3(2 * pairs), dim3(kThreads), Cfg::kSmemBytes, ctx.getStream(), mapX, mapW, p,
+				ctx.getDeviceStatus());
+		if (launched != cudaSuccess)
+			return convertStatus(launched);
 		return checkForErrors();
 	}
 
@@ -918,7 +952,10 @@ namespace
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
 		const int grid = std::min(p.num_tiles, sms);
-		kernel<<<grid, kThreads, Cfg::kSmemBytes, ctx.getStream()>>>(mapX, mapW, p, ctx.getDeviceStatus());
+		const cudaError_t launched = launch_chained(kernel, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, ctx.getStream(), mapX, mapW, p,
+				ctx.getDeviceStatus());
+		if (launched != cudaSuccess)
+			return convertStatus(launched);
 		return checkForErrors();
 	}
 
@@ -932,15 +969,14 @@ namespace
 		return enabled;
 	}
 
-	/* AVOCADO_B200_CONV=pair sends layers with more than 128 filters to the CTA-pair kernel.  It is off by default: on
-	 * the 256-channel int8 layer it was measured at 34.5 us against 30.3 us for the single-CTA kernel, whose pace is set
-	 * by the im2col copies of the pixel operand (the same in both), not by the filter copies the pair halves. */
+	/* AVOCADO_B200_CONV=single keeps every layer on the single-CTA kernel (for A/B timing); the default sends layers of
+	 * at least two 128-pixel blocks to the CTA-pair kernel */
 	bool pair_kernel_enabled()
 	{
 		static const bool enabled = []()
 		{
 			const char *env = std::getenv("AVOCADO_B200_CONV");
-			return env != nullptr and std::strcmp(env, "pair") == 0;
+			return not (env != nullptr and std::strcmp(env, "single") == 0);
 		}();
 		return enabled;
 	}
@@ -996,11 +1032,12 @@ namespace
 		}
 		const int taps = args.kernel_h * args.kernel_w;
 		const int block_n = (args.filters <= 64) ? 64 : (args.filters <= 128) ? 128 : 256;
+		const bool use_pair = pair_kernel_enabled() and pixels > kBlockM;
 		{
 			const uint64_t dims[2] = { static_cast<uint64_t>(taps) * args.channels, static_cast<uint64_t>(args.filters) };
 			const uint64_t strides[1] = { static_cast<uint64_t>(taps) * args.channels * elem };
 			/* the pair kernel copies the filter block in two halves, one per CTA */
-			const uint32_t box_rows = (block_n == 256 and pair_kernel_enabled()) ? static_cast<uint32_t>(kPairHalfN) : static_cast<uint32_t>(block_n);
+			const uint32_t box_rows = use_pair ? static_cast<uint32_t>(block_n / 2) : static_cast<uint32_t>(block_n);
 			const uint32_t box[2] = { static_cast<uint32_t>(block_channels), box_rows };
 			if (not umma::make_tensor_map(&mapW, Element<T>::kTma, 2, const_cast<void*>(args.w), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
 				return AVOCADO_STATUS_NOT_SUPPORTED;
@@ -1032,11 +1069,11 @@ namespace
 		switch (block_n)
 		{
 			case 64:
-				return launch_config<T, 64, 6>(ctx, mapX, mapW, p);
+				return use_pair ? launch_pair<T, 64, 2, 4>(ctx, mapX, mapW, p) : launch_config<T, 64, 6>(ctx, mapX, mapW, p);
 			case 128:
-				return launch_config<T, 128, 5>(ctx, mapX, mapW, p);
+				return use_pair ? launch_pair<T, 128, 2, 4>(ctx, mapX, mapW, p) : launch_config<T, 128, 5>(ctx, mapX, mapW, p);
 			default:
-				return pair_kernel_enabled() ? launch_pair<T, 6>(ctx, mapX, mapW, p) : launch_config<T, 256, 4>(ctx, mapX, mapW, p);
+				return use_pair ? launch_pair<T, 256, 2, 3>(ctx, mapX, mapW, p) : launch_config<T, 256, 4>(ctx, mapX, mapW, p);
 		}
 	}
 }

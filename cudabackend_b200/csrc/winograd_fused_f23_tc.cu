@@ -9,8 +9,8 @@
  *   y(tile) = A^T M A   (A^T is 2 x 4)      =>      y[a][b] = sum_nu ( sum_xi A^T[a][xi] M[xi][nu] ) A^T[b][nu]
  *
  * so the planes are taken in four groups of constant nu.  One work item = 128 tiles x 64 filters:
- *   warp 0      TMA producer: for nu, channel block: the four planes V[xi*4+nu] (128 tiles x 64 channels each) and
- *               U[xi*4+nu] (64 filters x 64 channels each) into one of two 128-byte-swizzled stages
+ *   warp 0      TMA producer: for nu, channel block, pair of xi: two planes V[xi*4+nu] (128 tiles x 64 channels each) and
+ *               U[xi*4+nu] (64 filters x 64 channels each) into one of four 128-byte-swizzled stages
  *   warp 1      one thread issues tcgen05.mma (M = 128, N = 64) into the group's four accumulators (4 x 64 TMEM columns);
  *               two groups fit TMEM, so the next group is contracted while the previous one is drained
  *   warps 2..9  drain a group (tcgen05.ld), apply the column transform over xi, and add the group's contribution to
@@ -38,12 +38,15 @@ namespace
 	constexpr int kBlockTiles = 128;
 	constexpr int kBlockFilters = 64;
 	constexpr int kBlockChannels = 64; /* 128 bytes of float16 */
-	/* A stage holds the operands of all four planes of a group for one block of 64 channels, and the MMAs of a stage are
-	 * issued contraction step outermost, plane innermost: consecutive MMAs go to different accumulators, and the producer
-	 * moves 96 KB per barrier round trip instead of 24 KB.  Measured on the 128 x 28 x 28 x 128 layer: 54 us with one plane
-	 * per stage (eight stages of 24 KB), 46 us with this form (two stages of 96 KB). */
-	constexpr int kStagePlanes = 4;
-	constexpr int kStages = 2;
+	/* A stage holds the operands of two of the four planes of a group for one block of 64 channels: four stages of 48 KB.
+	 * What sets the size: the thread that issues the MMAs pays about 100 cycles for a wait on a full barrier and 120 for a
+	 * commit, and no MMA of M = 128 retires in less than 86 cycles whatever its N, so a stage has to carry several MMAs
+	 * (eight here); and a stage stays occupied for the ~1700 cycles its copies take to land plus the time its MMAs run,
+	 * so the bytes in flight, not the size of a stage, bound the fill rate.  Measured on the 128 x 28 x 28 x 128 layer,
+	 * time per group of four planes inside the kernel: 4800 cycles with two stages of 96 KB (the whole group per stage:
+	 * only one stage is ever in flight while the other is read), 19 000 per item with eight stages of 24 KB. */
+	constexpr int kStagePlanes = 2;
+	constexpr int kStages = 4;
 	constexpr int kABytes = kBlockTiles * 128;
 	constexpr int kBBytes = kBlockFilters * 128;
 	constexpr int kStageBytes = kStagePlanes * (kABytes + kBBytes);
@@ -65,6 +68,7 @@ namespace
 			void *y;
 			float alpha1, alpha2, beta;
 			int activation;
+			int wide_stores; /* y is 32-byte aligned and K a multiple of 16: 16 filters of a pixel go out as one 32-byte store */
 	};
 
 	__device__ __noinline__ float activation_slow(avActivationType_t activation, float x)
@@ -89,6 +93,13 @@ namespace
 	__device__ __forceinline__ float2 unpack2(uint32_t raw, __nv_bfloat16)
 	{
 		return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw));
+	}
+
+	/* 32 bytes (16 values of a 16-bit type) with one instruction: a whole sector per lane */
+	__device__ __forceinline__ void store_256(void *dst, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t w4, uint32_t w5, uint32_t w6, uint32_t w7)
+	{
+		asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+				::"l"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(w4), "r"(w5), "r"(w6), "r"(w7) : "memory");
 	}
 
 	__device__ __forceinline__ void tmem_load_32x8(uint32_t taddr, float (&r)[8])
@@ -236,30 +247,31 @@ namespace
 					/* plain nested counters: this thread's own instruction latency bounds how fast stages can be issued, and an
 					 * integer division costs it more than the copy it is about to start */
 					for (int nu = 0; nu < 4 and ok; nu++)
-						for (int cb = 0; cb < p.channel_blocks; cb++)
-						{
-							if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
+						for (int cb = 0; cb < p.channel_blocks and ok; cb++)
+							for (int half = 0; half < 4 / kStagePlanes; half++)
 							{
-								umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
-								ok = false;
-								break;
-							}
-							uint8_t *a_dst = smem + stage * kStageBytes;
-							uint8_t *b_dst = a_dst + kStagePlanes * kABytes;
-							umma::mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+								if (not umma::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_ptr))
+								{
+									umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
+									ok = false;
+									break;
+								}
+								uint8_t *a_dst = smem + stage * kStageBytes;
+								uint8_t *b_dst = a_dst + kStagePlanes * kABytes;
+								umma::mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
 #pragma unroll
-							for (int xi = 0; xi < kStagePlanes; xi++)
-							{
-								const int plane = xi * 4 + nu;
-								umma::tma_load_3d(a_dst + xi * kABytes, &mapV, &full_bar[stage], cb * kBlockChannels, tb * kBlockTiles, plane);
-								umma::tma_load_3d(b_dst + xi * kBBytes, &mapU, &full_bar[stage], cb * kBlockChannels, fb * kBlockFilters, plane);
+								for (int j = 0; j < kStagePlanes; j++)
+								{
+									const int plane = (half * kStagePlanes + j) * 4 + nu;
+									umma::tma_load_3d(a_dst + j * kABytes, &mapV, &full_bar[stage], cb * kBlockChannels, tb * kBlockTiles, plane);
+									umma::tma_load_3d(b_dst + j * kBBytes, &mapU, &full_bar[stage], cb * kBlockChannels, fb * kBlockFilters, plane);
+								}
+								if (++stage == kStages)
+								{
+									stage = 0;
+									phase ^= 1u;
+								}
 							}
-							if (++stage == kStages)
-							{
-								stage = 0;
-								phase ^= 1u;
-							}
-						}
 				}
 			}
 		}
@@ -287,32 +299,32 @@ namespace
 						}
 						umma::tcgen05_fence_after();
 						const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kGroupColumns);
-						for (int cb = 0; cb < p.channel_blocks; cb++)
-						{
-							if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
+						for (int cb = 0; cb < p.channel_blocks and ok; cb++)
+							for (int half = 0; half < 4 / kStagePlanes; half++)
 							{
-								umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
-								ok = false;
-								break;
-							}
-							umma::tcgen05_fence_after();
-							/* the address field counts 16-byte units; a 16-element step along the contraction is 32 bytes of the
-							 * 128-byte swizzle row.  Contraction step outermost, plane innermost. */
-							const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kStageBytes / 16));
-							const uint64_t b_desc = a_desc + static_cast<uint64_t>(kStagePlanes * (kABytes / 16));
+								if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
+								{
+									umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
+									ok = false;
+									break;
+								}
+								umma::tcgen05_fence_after();
+								/* the address field counts 16-byte units; per plane the four 32-byte steps of the 128-byte swizzle row
+								 * go out as one instruction sequence */
+								static_assert(kBlockChannels / 16 == 4, "a plane's channel block is four MMAs deep");
+								const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kStageBytes / 16));
+								const uint64_t b_desc = a_desc + static_cast<uint64_t>(kStagePlanes * (kABytes / 16));
 #pragma unroll
-							for (int ks = 0; ks < kBlockChannels / 16; ks++)
-#pragma unroll
-								for (int xi = 0; xi < kStagePlanes; xi++)
-									umma::mma_f16(tmem_d + static_cast<uint32_t>(xi * kBlockFilters), a_desc + static_cast<uint64_t>(xi * (kABytes / 16) + 2 * ks),
-											b_desc + static_cast<uint64_t>(xi * (kBBytes / 16) + 2 * ks), idesc, cb != 0 or ks != 0);
-							umma::mma_commit(&empty_bar[stage]);
-							if (++stage == kStages)
-							{
-								stage = 0;
-								phase ^= 1u;
+								for (int j = 0; j < kStagePlanes; j++)
+									umma::mma_f16_k4(tmem_d + static_cast<uint32_t>((half * kStagePlanes + j) * kBlockFilters),
+											a_desc + static_cast<uint64_t>(j * (kABytes / 16)), b_desc + static_cast<uint64_t>(j * (kBBytes / 16)), idesc, cb != 0);
+								umma::mma_commit(&empty_bar[stage]);
+								if (++stage == kStages)
+								{
+									stage = 0;
+									phase ^= 1u;
+								}
 							}
-						}
 						if (ok)
 							umma::mma_commit(&tmem_full_bar[buf]);
 					}
@@ -403,6 +415,32 @@ namespace
 							continue;
 						const size_t index = ((static_cast<size_t>(n) * p.height + h) * p.width + w) * p.filters + k0;
 						T *dst = reinterpret_cast<T*>(p.y) + index;
+						if constexpr (SIMPLE)
+						{
+							/* a scattered 16-byte store costs the load/store unit as much as a 32-byte one: with whole blocks of
+							 * filters the thread's 32 values of this pixel leave as two 32-byte stores instead of four of 16 */
+							if (p.wide_stores != 0 and k0 + kFiltersPerThread <= p.filters)
+							{
+								const bool relu = activation == AVOCADO_ACTIVATION_RELU;
+#pragma unroll
+								for (int v = 0; v < kFiltersPerThread / 16; v++)
+								{
+									uint32_t packed[8];
+#pragma unroll
+									for (int q = 0; q < 8; q++)
+									{
+										const int j = 16 * v + 2 * q;
+										float r0 = fmaf(p.alpha1, out[a][b][j], bias_s[half_block * kFiltersPerThread + j]);
+										float r1 = fmaf(p.alpha1, out[a][b][j + 1], bias_s[half_block * kFiltersPerThread + j + 1]);
+										r0 = relu ? fmaxf(r0, 0.0f) : r0;
+										r1 = relu ? fmaxf(r1, 0.0f) : r1;
+										packed[q] = pack2(r0, r1, T());
+									}
+									store_256(dst + 16 * v, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+								}
+								continue;
+							}
+						}
 #pragma unroll
 						for (int v = 0; v < kFiltersPerThread / 8; v++)
 						{
@@ -561,6 +599,7 @@ namespace bk
 		p.alpha2 = getAlphaValue<float>(alpha2);
 		p.beta = getBetaValue<float>(beta);
 		p.activation = static_cast<int>(args.activation);
+		p.wide_stores = (args.filters % 16 == 0 and reinterpret_cast<uintptr_t>(args.y) % 32 == 0) ? 1 : 0;
 		if (yType == AVOCADO_DTYPE_FLOAT16)
 			return launch_typed<half>(ctx, mapV, mapU, p, deviceStatus);
 		return launch_typed<__nv_bfloat16>(ctx, mapV, mapU, p, deviceStatus);

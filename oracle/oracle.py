@@ -1,7 +1,7 @@
 """numpy front end of the CPU oracle (oracle/conv_oracle.c).  TEST INFRASTRUCTURE ONLY.
 
-Only tests/, __graft_entry__.smoke() and the cpu_baseline / reference arm of bench.py may import this module;
-the product (cudabackend_b200) never does.  Every function takes and returns numpy arrays in the layouts of the
+Only tests/, __graft_entry__.smoke() and bench.py (its cpu_baseline / reference arm, and the comparison of a timed
+step's output with this oracle outside the timed region) may import this module; the product (cudabackend_b200) never does.  Every function takes and returns numpy arrays in the layouts of the
 reference: activations NHWC, filters [K, kh, kw, C], transform-domain matrices [tile*tile, nbTiles, channels].
 """
 import ctypes

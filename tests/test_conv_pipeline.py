@@ -177,6 +177,22 @@ def test_int8_tensor_core_shapes(ctx, shape):
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("shape", [(3, 8, 16, 128, 64),    # 384 pixels: three 128-pixel blocks, the last pair's second CTA has no rows; 9 contraction blocks
+                                   (1, 15, 20, 256, 128),  # 300 pixels: the second CTA's block is partial; 18 contraction blocks, 128-filter tile
+                                   (2, 10, 13, 64, 272),   # 260 pixels, partial channel block (64 of 128), filters end inside the second 256-block
+                                   (5, 9, 9, 384, 16),     # 27 contraction blocks (odd: the last stage holds one block), smallest filter count
+                                   (2, 8, 8, 128, 256)])   # exactly 128 pixels: stays on the single-CTA kernel
+def test_int8_cta_pair_edges(ctx, shape):
+    """the CTA-pair kernel's own edges: odd block counts, stages that hold one contraction block instead of two, every
+    filter-tile width"""
+    n, h, w, c, k = shape
+    got, ref = int8_case(ctx, n, h, w, c, k, (5e-5, 2e-4), activation="relu", with_z=True)
+    assert np.array_equal(got, ref)
+    got, ref = int8_case(ctx, n, h, w, c, k, None, int32_output=True)
+    assert np.array_equal(got, ref)
+    assert ctx.last_device_status() == 0
+
+
 def test_int8_tensor_core_rotated_and_5x5(ctx):
     got, ref = int8_case(ctx, 8, 14, 14, 128, 64, (5e-5, 2e-4), rotated=True)
     assert np.array_equal(got, ref)

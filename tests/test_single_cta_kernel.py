@@ -1,10 +1,10 @@
-"""The CTA-pair (tcgen05 cta_group::2) implicit-GEMM kernel against the oracle.
+"""The single-CTA (tcgen05 cta_group::1) implicit-GEMM kernel against the oracle.
 
-The pair kernel is opt-in (environment AVOCADO_B200_CONV=pair, read once when the library first dispatches a
-convolution), so these cases run in a process of their own with that variable set.  They are the shapes of
-test_conv_pipeline.py that have more than 128 filters: a pixel count that is not a multiple of the 256-pixel tile (the
-second CTA of the last pair has nothing to store), filter counts that end inside a 256-filter block, more tiles than
-CTA pairs, and the 16-bit floating path.
+Layers of at least 256 output pixels run on the CTA-pair kernel (cta_group::2), which is what every other test of the
+implicit GEMM exercises; the single-CTA kernel then only sees layers of 129 to 255 pixels.  AVOCADO_B200_CONV=single
+(read once when the library first dispatches a convolution) keeps every layer on it, so these cases run in a process of
+their own with that variable set: a pixel count that is not a multiple of the 128-pixel tile, filter counts that end
+inside a 256-filter block and 64- and 128-filter tiles, more tiles than CTAs, and the 16-bit floating path.
 """
 import os
 import subprocess
@@ -24,7 +24,7 @@ from tests.test_conv_pipeline import int8_case
 
 api.load()
 ctx = api.Context(0)
-for shape in [(8, 14, 14, 256, 256), (16, 7, 9, 384, 272), (32, 28, 28, 128, 256)]:
+for shape in [(8, 14, 14, 256, 256), (16, 7, 9, 384, 272), (32, 28, 28, 128, 256), (8, 14, 14, 128, 64), (4, 9, 9, 64, 128)]:
     got, ref = int8_case(ctx, *shape, (5e-5, 2e-4), activation="relu", with_z=True)
     assert np.array_equal(got, ref), ("int8", shape)
     got, ref = int8_case(ctx, *shape, (1e-3, 1e-2))
@@ -42,14 +42,14 @@ for dtype, bound in (("float16", 1.5e-3), ("bfloat16", 1e-2)):
     assert err <= bound, (dtype, err)
 ctx.synchronize()
 assert ctx.last_device_status() == 0
-print("pair kernel cases passed")
+print("single-CTA kernel cases passed")
 """
 
 
-def test_pair_kernel_matches_the_oracle(library, device_count):
+def test_single_cta_kernel_matches_the_oracle(library, device_count):
     if device_count == 0:
         pytest.skip("no CUDA device visible")
-    env = dict(os.environ, AVOCADO_B200_CONV="pair")
+    env = dict(os.environ, AVOCADO_B200_CONV="single")
     result = subprocess.run([sys.executable, "-c", CASES], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert result.returncode == 0, (result.stdout[-1000:], result.stderr[-3000:])
-    assert "pair kernel cases passed" in result.stdout
+    assert "single-CTA kernel cases passed" in result.stdout
