@@ -278,7 +278,9 @@ namespace f43
 	};
 
 	template<int TS, typename T, typename MT>
-	/* the halo ring (up to 96 KB per block) lets two blocks share an SM: give each the registers of half an SM (no spills) */
+	/* the halo ring (up to 96 KB per block) lets two blocks share an SM: give each the registers of half an SM (no spills).
+	 * Three blocks of 80 registers spill about 90 bytes per thread and were measured slower (25.5 against 19.0 us on the
+	 * 64 x 56 x 56 x 64 float16 layer). */
 	__global__ void __launch_bounds__(kThreads, 2) kernel_input_tma(const __grid_constant__ CUtensorMap mapX, MT *__restrict__ matrices, InputGeometry g,
 			int *deviceStatus, WeightJob weightJob)
 	{
@@ -295,7 +297,7 @@ namespace f43
 		extern __shared__ uint8_t smem_raw[];
 		uint8_t *smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
 		__shared__ __align__(8) uint64_t full_bar[kMaxStages];
-		__shared__ int go_flag;
+		__shared__ __align__(8) uint64_t empty_bar[kMaxStages];
 		__shared__ int abort_flag;
 
 		const int tid = threadIdx.x;
@@ -306,7 +308,10 @@ namespace f43
 		{
 			abort_flag = 0;
 			for (int i = 0; i < kMaxStages; i++)
+			{
 				umma::mbar_init(&full_bar[i], 1);
+				umma::mbar_init(&empty_bar[i], static_cast<uint32_t>(nwarps));
+			}
 			umma::mbar_fence_init();
 			umma::prefetch_tensormap(&mapX);
 		}
@@ -334,8 +339,12 @@ namespace f43
 					issue(static_cast<int>(item), i);
 			}
 
+		/* No block-wide barrier inside the loop: every warp waits for a strip on its full barrier by itself and hands the
+		 * buffer back on its empty barrier as soon as its tile sits in registers, i.e. before the second transform pass and
+		 * the stores, so the refill of a buffer overlaps the arithmetic on what it held and warps drift apart freely. */
 		const size_t plane_stride = static_cast<size_t>(g.nb_tiles) * g.channels;
 		const int row_pitch = g.box_w * kChannelBlock; /* elements of T per box row */
+		volatile int *abort_ptr = &abort_flag;
 		int it = 0;
 		for (int item = cta; item < g.num_items; item += ncta, it++)
 		{
@@ -343,19 +352,26 @@ namespace f43
 			const uint32_t phase = static_cast<uint32_t>(it / g.stages) & 1u;
 			if (tid == 0)
 			{
-				/* the buffer consumed in the previous iteration was released by the barrier that closed it */
+				/* the strip stages-1 ahead goes into the buffer of the previous iteration, once every warp has let go of it */
 				const long long next = static_cast<long long>(item) + static_cast<long long>(g.stages - 1) * ncta;
 				if (next < g.num_items)
-					issue(static_cast<int>(next), (it + g.stages - 1) % g.stages);
-				const bool ready = umma::mbar_wait(&full_bar[stage], phase, &abort_flag);
-				if (not ready)
-					umma::raise_error(&abort_flag, deviceStatus, umma::kErrorTmaWait);
-				go_flag = ready ? 1 : 0;
+				{
+					const int refill = (it + g.stages - 1) % g.stages;
+					bool free_now = true;
+					if (it >= 1)
+						free_now = umma::mbar_wait(&empty_bar[refill], static_cast<uint32_t>((it - 1) / g.stages) & 1u, abort_ptr);
+					if (free_now)
+						issue(static_cast<int>(next), refill);
+					else
+						umma::raise_error(abort_ptr, deviceStatus, umma::kErrorStageWait);
+				}
 			}
-			__syncthreads();
-			if (go_flag == 0)
+			__syncwarp();
+			if (not umma::mbar_wait(&full_bar[stage], phase, abort_ptr))
+			{
+				umma::raise_error(abort_ptr, deviceStatus, umma::kErrorTmaWait);
 				break;
-			umma::mbar_try_wait(&full_bar[stage], phase); /* completed phase: returns at once, orders this thread after the copy */
+			}
 
 			const int cb = item % g.c_blocks;
 			const int ws = (item / g.c_blocks) % g.w_segments;
@@ -365,50 +381,70 @@ namespace f43
 			const T *box = reinterpret_cast<const T*>(smem + stage * g.stage_bytes);
 
 			const int strip_tiles = g.strip_tiles_h * g.strip_tiles_w;
+			bool released = false;
 			for (int t = warp; t < strip_tiles; t += nwarps)
 			{
 				const int tr = t / g.strip_tiles_w;
 				const int tc = t - tr * g.strip_tiles_w;
 				const int th = rg * g.strip_tiles_h + tr;
 				const int tw = ws * g.strip_tiles_w + tc;
-				if (th >= g.tiles_h or tw >= g.tiles_w or c0 >= g.channels)
-					continue;
+				const bool active = th < g.tiles_h and tw < g.tiles_w and c0 < g.channels;
 				constexpr int TL = TS + 2;
 				const T *src = box + (tr * TS) * row_pitch + (tc * TS) * kChannelBlock + 2 * lane;
 
 				f2 tmp[TL * TL]; /* B^T d, both channels of the lane */
-#pragma unroll
-				for (int c = 0; c < TL; c++)
+				if (active)
 				{
-					f2 col[TL], o[TL];
-#pragma unroll
-					for (int r = 0; r < TL; r++)
-						col[r] = load_pair<T>(src + r * row_pitch + c * kChannelBlock);
-					input_1d(col, o);
-#pragma unroll
-					for (int i = 0; i < TL; i++)
-						tmp[i * TL + c] = o[i];
-				}
-				const long long tile = (static_cast<long long>(n) * g.tiles_h + th) * g.tiles_w + tw;
-				MT *dst = matrices + static_cast<size_t>(tile) * g.channels + c0;
-#pragma unroll
-				for (int i = 0; i < TL; i++)
-				{
-					f2 row[TL], o[TL];
 #pragma unroll
 					for (int c = 0; c < TL; c++)
-						row[c] = tmp[i * TL + c];
-					input_1d(row, o);
-#pragma unroll
-					for (int j = 0; j < TL; j++)
 					{
-						store_pair<MT>(dst, o[j]);
-						dst += plane_stride;
+						f2 col[TL], o[TL];
+#pragma unroll
+						for (int r = 0; r < TL; r++)
+							col[r] = load_pair<T>(src + r * row_pitch + c * kChannelBlock);
+						input_1d(col, o);
+#pragma unroll
+						for (int i = 0; i < TL; i++)
+							tmp[i * TL + c] = o[i];
+					}
+				}
+				if (t + nwarps >= strip_tiles)
+				{
+					/* this warp's last tile of the strip is in registers */
+					__syncwarp();
+					if (lane == 0)
+						umma::mbar_arrive(&empty_bar[stage]);
+					released = true;
+				}
+				if (active)
+				{
+					const long long tile = (static_cast<long long>(n) * g.tiles_h + th) * g.tiles_w + tw;
+					MT *dst = matrices + static_cast<size_t>(tile) * g.channels + c0;
+#pragma unroll
+					for (int i = 0; i < TL; i++)
+					{
+						f2 row[TL], o[TL];
+#pragma unroll
+						for (int c = 0; c < TL; c++)
+							row[c] = tmp[i * TL + c];
+						input_1d(row, o);
+#pragma unroll
+						for (int j = 0; j < TL; j++)
+						{
+							store_pair<MT>(dst, o[j]);
+							dst += plane_stride;
+						}
 					}
 				}
 			}
-			__syncthreads(); /* every warp is done with this buffer: it may be refilled */
+			if (not released)
+			{
+				__syncwarp();
+				if (lane == 0)
+					umma::mbar_arrive(&empty_bar[stage]); /* a warp without a tile in this strip */
+			}
 		}
+		__syncthreads();
 		if (abort_flag != 0)
 			umma::drain_after_abort();
 	}
