@@ -44,6 +44,12 @@ CONFIGS = {
             kind="implicit_gemm"),
     5: dict(name="cfg5: training step (fwd + dX + dW) NHWC float32, 56x56 C=K=64, non-fused Winograd F(4x4,3x3)", n=256, h=56, w=56, c=64, k=64,
             dtype="float32", kind="training"),
+    # the layers of cfg 2 and cfg 3 through cudaConvolutionImplicitGemmForward: not baseline configurations, reported beside them
+    # because on this machine the direct algorithm is the faster way to the same convolution
+    12: dict(name="the layer of cfg2 (N=64 56x56 C=K=64 float16, + bias) through the implicit-GEMM entry point", n=64, h=56, w=56, c=64, k=64,
+             dtype="float16", kind="implicit_gemm"),
+    13: dict(name="the layer of cfg3 (N=128 28x28 C=K=128 bfloat16, + bias + ReLU) through the implicit-GEMM entry point", n=128, h=28, w=28,
+             c=128, k=128, dtype="bfloat16", kind="implicit_gemm", activation="relu"),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the committed ncu captures under
@@ -208,7 +214,7 @@ def cpu_baseline(cfg, sample_images, target_seconds=12.0, max_passes=60):
 def run_reference_arm(args, cfg, rank):
     if rank != 0:
         return
-    images = {2: 16, 3: 16, 4: 16, 5: 4}[args.config]
+    images = {2: 16, 3: 16, 4: 16, 5: 4, 12: 16, 13: 16}[args.config]
     for _ in range(args.warmup):
         cpu_sample(cfg, max(1, images // 4))
     total_s, total_flops = 0.0, 0.0
@@ -300,7 +306,7 @@ class Workload:
             return [("forward", p.forward), ("backward_weights", lambda: p.backward_weights(reuse_v=True)), ("backward_data", p.backward_data)]
         if kind == "winograd_fused":
             return [("winograd_fused", lambda: p.winograd_fused(activation="relu"))]
-        return [("implicit_gemm", p.implicit_gemm)]
+        return [("implicit_gemm", lambda: p.implicit_gemm(activation=self.cfg.get("activation", "linear")))]
 
     def step(self):
         kind = self.cfg["kind"]
@@ -679,7 +685,7 @@ class Measurement:
         if kind == "winograd_nonfused":
             ref = o.conv2d_forward(s["x"], s["w"])
         else:
-            ref = o.conv2d_forward(s["x"], s["w"], bias=s["b"], activation="relu" if kind == "winograd_fused" else "linear")
+            ref = o.conv2d_forward(s["x"], s["w"], bias=s["b"], activation="relu" if kind == "winograd_fused" else cfg.get("activation", "linear"))
         err = o.error_metrics(ws.p.y.download(ctx), ref)
         tolerance = TOLERANCE[cfg["dtype"]]
         note = None
@@ -807,7 +813,7 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
         tensor_peak, source = 2.0 * peaks["bf16_tflops"], peaks["source"] + " bf16 x2 (nominal int8 ratio; the int8 yardstick failed here)"
     else:
         tensor_peak, source = peaks["bf16_tflops"], peaks["source"]
-    return {"kernel": "kernel_implicit_gemm_tc", "bound": "tensor", "achieved": ops, "peak": tensor_peak, "unit": "TOP/s" if cfg["dtype"] == "int8" else "TFLOP/s",
+    return {"kernel": "kernel_implicit_gemm_tc_pair (cta_group::2)", "bound": "tensor", "achieved": ops, "peak": tensor_peak, "unit": "TOP/s" if cfg["dtype"] == "int8" else "TFLOP/s",
             "frac": ops / tensor_peak, "traffic": None, "operations": flops, "algorithmic_bytes": total, "peak_source": source,
             "hbm_gbs": total / step_s / 1e9}
 
@@ -1061,8 +1067,9 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     # ---- the other configurations, each rank its own batch of the configured size -------------------------
     if not args.only_headline and args.config == 2 and args.matrices is None:
         configs = {}
-        for key, config_id, matrices in (("cfg2_float32_matrices", 2, "float32"), ("cfg3", 3, None), ("cfg4", 4, None), ("cfg5", 5, None)):
-            if world > 1 and config_id == 5:
+        for key, config_id, matrices in (("cfg2_float32_matrices", 2, "float32"), ("cfg3", 3, None), ("cfg4", 4, None), ("cfg5", 5, None),
+                                         ("cfg2_layer_implicit_gemm", 12, None), ("cfg3_layer_implicit_gemm", 13, None)):
+            if world > 1 and config_id in (5, 12, 13):
                 continue  # on several GPUs the training step is the batch-sharded record with the all-reduce (`sharded.cfg5_allreduce`)
             # parity and the sustained replay are single-GPU properties, measured at N = 1; at N > 1 the sub-records are the
             # weak-scaling throughput of each configuration
@@ -1101,7 +1108,7 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
 
     if rank == 0:
         if world == 1 and not args.no_cpu:
-            images = {2: 64, 3: 64, 4: 64, 5: 16}[args.config]
+            images = {2: 64, 3: 64, 4: 64, 5: 16, 12: 64, 13: 64}[args.config]
             line["cpu_baseline"] = cpu_baseline(cfg, images)
         sampler.stop()
         print(json.dumps(line))
@@ -1116,7 +1123,8 @@ def main():
     parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS), help="the headline workload")
+    parser.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS),
+                        help="the headline workload: 2..5 are the baseline's configurations; 12 and 13 are the layers of 2 and 3 through the implicit GEMM")
     parser.add_argument("--matrices", default=None, choices=["float16", "bfloat16", "float32"], help="dtype of the transform-domain tensors")
     parser.add_argument("--rotation", type=int, default=4, help="buffer sets rotated between steps")
     parser.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained replay of each configuration")

@@ -9,7 +9,9 @@
  *   A operand     never materialised: for each (tap, channel block) a TMA copy in im2col mode gathers 128
  *                 consecutive output pixels' input vectors (128 bytes each) straight from the NHWC tensor into
  *                 128-byte-swizzled shared memory; pixels that fall outside the image arrive as zeros (= padding)
- *   B operand     the filters [K, kh*kw*C], already contiguous along the contraction: tiled TMA copy
+ *   B operand     the filters [K, kh*kw, C], contiguous along the contraction: tiled TMA copy of one tap's channel
+ *                 block of N filters (a three-dimensional map, so that channels past the end of a partial block
+ *                 arrive as zeros like those of the pixels)
  *   MMA           tcgen05.mma, N = 64/128/256; kind::i8 with int32 accumulation for int8, kind::f16 with float32
  *                 accumulation for float16 / bfloat16; accumulator double-buffered in TMEM.  Layers of at least 256
  *                 output pixels run on CTA pairs (cta_group::2, M = 256, each CTA holding half of the filter block),
@@ -453,7 +455,7 @@ namespace
 						umma::mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
 						umma::tma_load_im2col_4d(a_dst, &mapX, &full_bar[stage], cb * kElemsPerBlock, ow + p.pad_w, oh + p.pad_h, n, static_cast<uint16_t>(s),
 								static_cast<uint16_t>(r));
-						umma::tma_load_2d(b_dst, &mapW, &full_bar[stage], wtap * p.channels + cb * kElemsPerBlock, nb * BLOCK_N);
+						umma::tma_load_3d(b_dst, &mapW, &full_bar[stage], cb * kElemsPerBlock, wtap, nb * BLOCK_N);
 						if (++stage == STAGES)
 						{
 							stage = 0;
@@ -744,7 +746,7 @@ namespace
 								uint8_t *b_dst = a_dst + Cfg::kABytes;
 								umma::tma_load_im2col_4d_pair(a_dst, &mapX, bar, cb * kElemsPerBlock, ow + p.pad_w, oh + p.pad_h, n, static_cast<uint16_t>(s),
 										static_cast<uint16_t>(r));
-								umma::tma_load_2d_pair(b_dst, &mapW, bar, wtap * p.channels + cb * kElemsPerBlock, filter0);
+								umma::tma_load_3d_pair(b_dst, &mapW, bar, cb * kElemsPerBlock, wtap, filter0);
 								if (++cb == p.c_blocks)
 								{
 									cb = 0;
@@ -987,15 +989,10 @@ namespace
 		const int elem = static_cast<int>(sizeof(T));
 		const int block_channels = kBlockKBytes / elem;
 		/* Shapes the kernel covers; everything else goes to the direct kernel.  The channel count need not fill whole
-		 * 128-byte blocks: the im2col copy fills the channels past the end of a pixel with zeros, and whatever the filter
-		 * copy fetches for those columns (the first channels of the next tap, or zeros past the end of the row) is
-		 * multiplied by them.  What TMA needs is 16-byte row pitches: C and kh*kw*C times the element size. */
-		const int taps_all = args.kernel_h * args.kernel_w;
-		if ((args.channels * elem) % 16 != 0 or (static_cast<long long>(taps_all) * args.channels * elem) % 16 != 0)
-			return AVOCADO_STATUS_NOT_SUPPORTED;
-		/* with floating-point filters a non-finite value in the next tap would turn that zero product into NaN: keep
-		 * partial blocks for the integer case, where it cannot happen, and for float filters only when blocks are whole */
-		if (not Element<T>::kInteger and args.channels % block_channels != 0)
+		 * 128-byte blocks: both copies (im2col pixels, and filters through a map whose innermost dimension is the channels
+		 * of ONE tap) fill the channels past the end with zeros.  What TMA needs is 16-byte pitches: C times the element
+		 * size. */
+		if ((args.channels * elem) % 16 != 0)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		const int out_align = Element<T>::kInteger ? 16 : 8;
 		if (args.filters % out_align != 0 or args.filters < 16)
@@ -1034,12 +1031,12 @@ namespace
 		const int block_n = (args.filters <= 64) ? 64 : (args.filters <= 128) ? 128 : 256;
 		const bool use_pair = pair_kernel_enabled() and pixels > kBlockM;
 		{
-			const uint64_t dims[2] = { static_cast<uint64_t>(taps) * args.channels, static_cast<uint64_t>(args.filters) };
-			const uint64_t strides[1] = { static_cast<uint64_t>(taps) * args.channels * elem };
+			const uint64_t dims[3] = { static_cast<uint64_t>(args.channels), static_cast<uint64_t>(taps), static_cast<uint64_t>(args.filters) };
+			const uint64_t strides[2] = { static_cast<uint64_t>(args.channels) * elem, static_cast<uint64_t>(taps) * args.channels * elem };
 			/* the pair kernel copies the filter block in two halves, one per CTA */
 			const uint32_t box_rows = use_pair ? static_cast<uint32_t>(block_n / 2) : static_cast<uint32_t>(block_n);
-			const uint32_t box[2] = { static_cast<uint32_t>(block_channels), box_rows };
-			if (not umma::make_tensor_map(&mapW, Element<T>::kTma, 2, const_cast<void*>(args.w), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+			const uint32_t box[3] = { static_cast<uint32_t>(block_channels), 1u, box_rows };
+			if (not umma::make_tensor_map(&mapW, Element<T>::kTma, 3, const_cast<void*>(args.w), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
 				return AVOCADO_STATUS_NOT_SUPPORTED;
 		}
 

@@ -313,6 +313,11 @@ namespace umma
 		asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4}], [%2];"
 				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c0), "r"(c1) : "memory");
 	}
+	__device__ __forceinline__ void tma_load_3d_pair(void *smemDst, const CUtensorMap *map, uint32_t barClusterAddr, int c0, int c1, int c2)
+	{
+		asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4, %5}], [%2];"
+				::"r"(smem_u32(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c0), "r"(c1), "r"(c2) : "memory");
+	}
 	__device__ __forceinline__ void tma_load_im2col_4d_pair(void *smemDst, const CUtensorMap *map, uint32_t barClusterAddr, int c, int w, int h, int n,
 			uint16_t offW, uint16_t offH)
 	{

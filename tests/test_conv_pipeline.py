@@ -270,6 +270,23 @@ def test_int8_tensor_core_small_and_partial_channel_blocks(ctx, shape):
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(2, 14, 14, 40, 64), (3, 10, 11, 72, 24), (2, 16, 16, 8, 16), (1, 20, 20, 200, 136)])
+def test_implicit_gemm_16bit_partial_channel_blocks(ctx, dtype, shape):
+    """16-bit layers whose channel count does not fill the kernel's 64-channel blocks (C = 40, 72, 8, 200): the filter map
+    has the channels of one tap as its innermost dimension, so the columns past C arrive as zeros for filters and pixels
+    alike and the layer stays on the tensor cores"""
+    n, h, w, c, k = shape
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, dtype)
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+    b = d.set_bias(common.uniform("b", (k,), -0.1, 0.1))
+    d.implicit_gemm(activation="relu")
+    ref = o.conv2d_forward(x, wt, bias=b, activation="relu")
+    assert o.error_metrics(d.y.download(ctx), ref)["elem"] <= {"float16": 1.5e-3, "bfloat16": 1e-2}[dtype]
+    assert ctx.last_device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(4, 28, 28, 64, 64), (2, 9, 10, 24, 16), (3, 14, 15, 128, 72), (2, 8, 8, 16, 8)])
 def test_implicit_gemm_float32_on_tensor_cores(ctx, shape):
     """float32 through cudaConvolutionImplicitGemmForward: lowered (im2row) onto the 3xTF32 tcgen05 GEMM, with the whole
