@@ -54,7 +54,10 @@ CONFIGS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the committed ncu captures under
 # profiles/ (cold caches, one launch): (config, matrices dtype, fused contraction + output transform) -> bytes
-NCU_TRAFFIC = {(2, "float16", False): 58.124e6 + 10.220e6}
+NCU_TRAFFIC = {(2, "float16", False): 58.123e6 + 8.522e6,    # kernel_gemm_nt_tc (the written M mostly still sits in L2 when the capture ends)
+               (2, "float16", True): 58.172e6 + 3.234e6,     # kernel_f43_contract_output
+               (3, "bfloat16", False): 103.361e6 + 6.278e6,  # kernel_f23_contract_output
+               (4, "int8", False): 13.514e6}                 # kernel_implicit_gemm_tc_pair (the int8 output stays in L2)
 
 # what the error figure of a floating-point configuration is judged against: max |err| / max(|ref|, rms(ref))
 TOLERANCE = {"float32": 1e-3, "float16": 1e-2, "bfloat16": 1e-2}
@@ -795,8 +798,8 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
         moved = moved_bytes_fused_winograd(cfg)
         achieved = total / step_s / 1e9
         return {"kernel": "weight transform, input transform, kernel_f23_contract_output (contraction + output transform; M stays in TMEM)",
-                "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                "algorithmic_bytes": total, "moved_bytes_model": moved, "moved_over_algorithmic": moved / total,
+                "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "traffic": NCU_TRAFFIC.get((m.config_id, cfg["dtype"], False)), "algorithmic_bytes": total, "moved_bytes_model": moved, "moved_over_algorithmic": moved / total,
                 "frac_on_moved_bytes": moved / step_s / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
                 "tensor_tflops_effective": flops / step_s / 1e12}
     if kind == "training":
@@ -814,7 +817,7 @@ def roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks, copy_reference=N
     else:
         tensor_peak, source = peaks["bf16_tflops"], peaks["source"]
     return {"kernel": "kernel_implicit_gemm_tc_pair (cta_group::2)", "bound": "tensor", "achieved": ops, "peak": tensor_peak, "unit": "TOP/s" if cfg["dtype"] == "int8" else "TFLOP/s",
-            "frac": ops / tensor_peak, "traffic": None, "operations": flops, "algorithmic_bytes": total, "peak_source": source,
+            "frac": ops / tensor_peak, "traffic": NCU_TRAFFIC.get((m.config_id, cfg["dtype"], False)), "operations": flops, "algorithmic_bytes": total, "peak_source": source,
             "hbm_gbs": total / step_s / 1e9}
 
 
