@@ -311,6 +311,13 @@ class Workload:
             return [("winograd_fused", lambda: p.winograd_fused(activation="relu"))]
         return [("implicit_gemm", lambda: p.implicit_gemm(activation=self.cfg.get("activation", "linear")))]
 
+    def forward_kernels(self):
+        """The four calls of the forward chain one by one (training configuration: the transforms at a size where launch and
+        ramp no longer dominate)."""
+        p = self.p
+        return [("weight_transform", p.weight_transform), ("input_transform", p.input_transform), ("gemm", lambda: p.gemm(p.v, p.u, p.m, False, True)),
+                ("output_transform", p.output_transform)]
+
     def step(self):
         kind = self.cfg["kind"]
         if kind == "winograd_nonfused":
@@ -611,14 +618,15 @@ class Measurement:
             record["us_x_mhz"] = ms_per_step * 1e3 * clocks["sm_mhz"]
         return record
 
-    def stage_times(self, reps):
+    def stage_times(self, reps, forward_kernels=False):
         """Per-kernel durations: each stage launched back to back over the rotating buffer sets, CUDA events around."""
         torch = self.torch
         self.use_shared_context()
-        names = [name for name, _ in self.sets[0].stages()]
+        stages_of = (lambda ws: ws.forward_kernels()) if forward_kernels else (lambda ws: ws.stages())
+        names = [name for name, _ in stages_of(self.sets[0])]
         out = {}
         for j, name in enumerate(names):
-            fns = [ws.stages()[j][1] for ws in self.sets]
+            fns = [stages_of(ws)[j][1] for ws in self.sets]
             for fn in fns:
                 fn()
             e0 = torch.cuda.Event(enable_timing=True)
@@ -842,6 +850,14 @@ def sub_config(args, config_id, matrices, rank, world, local_rank, peaks, lib_pe
               "gpu_launches": m.sets[0].launches_per_step() * done, "launch_mode": launch_mode(args, steps_per_graph), "clocks": clocks}
     if stage_ms:
         record["stage_ms"] = stage_ms
+    if want_stages and cfg["kind"] == "training":
+        # the forward chain kernel by kernel: the same transforms as cfg 2 on 8x the bytes
+        kernel_ms = m.stage_times(20, forward_kernels=True)
+        sb = stage_bytes(cfg, "float32")
+        record["forward_kernel_ms"] = kernel_ms
+        record["forward_kernel_hbm_frac"] = {name: sb[name] / (kernel_ms[name] * 1e-3) / 1e9 / peaks["hbm_gbs"] for name in kernel_ms}
+        record["forward_kernel_note"] = ("algorithmic bytes of each call / its duration / the measured copy rate; above 1.0 when the tensor just "
+                                         "written by the call before is still partly in the 126 MB L2")
     if rank == 0:
         record["roofline"] = roofline_record(m, ms_per_step, stage_ms, peaks, lib_peaks)
     if want_sustained:
