@@ -211,7 +211,53 @@ namespace f43
 		*reinterpret_cast<unsigned long long*>(ptr) = value.v;
 	}
 
-	constexpr int kChannelBlock = 64; /* channels per strip: one warp, two channels per lane */
+	/* Q adjacent pairs (2Q channels) of a lane with one access: 4, 8 or 16 bytes */
+	template<typename T, int Q>
+	__device__ __forceinline__ void load_pairs(const T *ptr, f2 (&out)[Q])
+	{
+		if constexpr (Q == 1)
+			out[0] = load_pair<T>(ptr);
+		else
+		{
+			static_assert(Q == 2, "one or two pairs per lane");
+			using P = typename Pair<T>::type;
+			if constexpr (sizeof(P) == 4)
+			{
+				const uint2 raw = *reinterpret_cast<const uint2*>(ptr);
+				out[0] = unpack_pair<T>(*reinterpret_cast<const P*>(&raw.x));
+				out[1] = unpack_pair<T>(*reinterpret_cast<const P*>(&raw.y));
+			}
+			else
+			{
+				const float4 raw = *reinterpret_cast<const float4*>(ptr);
+				out[0] = make_f2(raw.x, raw.y);
+				out[1] = make_f2(raw.z, raw.w);
+			}
+		}
+	}
+	template<typename T, int Q>
+	__device__ __forceinline__ void store_pairs(T *ptr, const f2 (&value)[Q]) /* each value rounded once, to nearest even */
+	{
+		if constexpr (Q == 1)
+			store_pair<T>(ptr, value[0]);
+		else
+		{
+			using P = typename Pair<T>::type;
+			const float2 a = to_float2(value[0]), b = to_float2(value[1]);
+			if constexpr (sizeof(P) == 4)
+			{
+				const P pa = Pair<T>::pack(a.x, a.y), pb = Pair<T>::pack(b.x, b.y);
+				uint2 raw;
+				raw.x = *reinterpret_cast<const uint32_t*>(&pa);
+				raw.y = *reinterpret_cast<const uint32_t*>(&pb);
+				*reinterpret_cast<uint2*>(ptr) = raw;
+			}
+			else
+				*reinterpret_cast<float4*>(ptr) = make_float4(a.x, a.y, b.x, b.y);
+		}
+	}
+
+	constexpr int kChannelBlock = 64; /* channels per strip and pair of a lane: one warp, two channels per lane and pair */
 	constexpr int kThreads = 256;
 	constexpr int kMaxStages = 4;
 #ifndef F43_OUT_BLOCKS
@@ -277,7 +323,9 @@ namespace f43
 			long long nb_tiles;
 	};
 
-	template<int TS, typename T, typename MT>
+	/* Q = pairs of channels per lane: 1 (a warp covers 64 channels of a tile) or 2 (128 channels: half as many shared
+	 * loads, stores and address computations per byte; the tile's registers double, which F(2x2) affords and F(4x4) does not) */
+	template<int TS, typename T, typename MT, int Q>
 	/* the halo ring (up to 96 KB per block) lets two blocks share an SM: give each the registers of half an SM (no spills).
 	 * Three blocks of 80 registers spill about 90 bytes per thread and were measured slower (25.5 against 19.0 us on the
 	 * 64 x 56 x 56 x 64 float16 layer). */
@@ -326,7 +374,7 @@ namespace f43
 			const int rg = (item / (g.c_blocks * g.w_segments)) % g.row_groups;
 			const int n = item / (g.c_blocks * g.w_segments * g.row_groups);
 			umma::mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>(g.stage_bytes));
-			umma::tma_load_4d(smem + stage * g.stage_bytes, &mapX, &full_bar[stage], cb * kChannelBlock, g.pad_w + ws * g.strip_tiles_w * TS,
+			umma::tma_load_4d(smem + stage * g.stage_bytes, &mapX, &full_bar[stage], cb * kChannelBlock * Q, g.pad_w + ws * g.strip_tiles_w * TS,
 					g.pad_h + rg * g.strip_tiles_h * TS, n);
 		};
 
@@ -343,7 +391,9 @@ namespace f43
 		 * buffer back on its empty barrier as soon as its tile sits in registers, i.e. before the second transform pass and
 		 * the stores, so the refill of a buffer overlaps the arithmetic on what it held and warps drift apart freely. */
 		const size_t plane_stride = static_cast<size_t>(g.nb_tiles) * g.channels;
-		const int row_pitch = g.box_w * kChannelBlock; /* elements of T per box row */
+		constexpr int kLaneChannels = 2 * Q;
+		constexpr int kWarpChannels = kChannelBlock * Q;
+		const int row_pitch = g.box_w * kWarpChannels; /* elements of T per box row */
 		volatile int *abort_ptr = &abort_flag;
 		int it = 0;
 		for (int item = cta; item < g.num_items; item += ncta, it++)
@@ -377,7 +427,7 @@ namespace f43
 			const int ws = (item / g.c_blocks) % g.w_segments;
 			const int rg = (item / (g.c_blocks * g.w_segments)) % g.row_groups;
 			const int n = item / (g.c_blocks * g.w_segments * g.row_groups);
-			const int c0 = cb * kChannelBlock + 2 * lane;
+			const int c0 = cb * kWarpChannels + kLaneChannels * lane;
 			const T *box = reinterpret_cast<const T*>(smem + stage * g.stage_bytes);
 
 			const int strip_tiles = g.strip_tiles_h * g.strip_tiles_w;
@@ -390,22 +440,33 @@ namespace f43
 				const int tw = ws * g.strip_tiles_w + tc;
 				const bool active = th < g.tiles_h and tw < g.tiles_w and c0 < g.channels;
 				constexpr int TL = TS + 2;
-				const T *src = box + (tr * TS) * row_pitch + (tc * TS) * kChannelBlock + 2 * lane;
+				const T *src = box + (tr * TS) * row_pitch + (tc * TS) * kWarpChannels + kLaneChannels * lane;
 
-				f2 tmp[TL * TL]; /* B^T d, both channels of the lane */
+				f2 tmp[Q][TL * TL]; /* B^T d, the lane's pairs of channels */
 				if (active)
 				{
 #pragma unroll
 					for (int c = 0; c < TL; c++)
 					{
-						f2 col[TL], o[TL];
+						f2 col[Q][TL];
 #pragma unroll
 						for (int r = 0; r < TL; r++)
-							col[r] = load_pair<T>(src + r * row_pitch + c * kChannelBlock);
-						input_1d(col, o);
+						{
+							f2 loaded[Q];
+							load_pairs<T, Q>(src + r * row_pitch + c * kWarpChannels, loaded);
 #pragma unroll
-						for (int i = 0; i < TL; i++)
-							tmp[i * TL + c] = o[i];
+							for (int q = 0; q < Q; q++)
+								col[q][r] = loaded[q];
+						}
+#pragma unroll
+						for (int q = 0; q < Q; q++)
+						{
+							f2 o[TL];
+							input_1d(col[q], o);
+#pragma unroll
+							for (int i = 0; i < TL; i++)
+								tmp[q][i * TL + c] = o[i];
+						}
 					}
 				}
 				if (t + nwarps >= strip_tiles)
@@ -423,15 +484,24 @@ namespace f43
 #pragma unroll
 					for (int i = 0; i < TL; i++)
 					{
-						f2 row[TL], o[TL];
+						f2 o[Q][TL];
 #pragma unroll
-						for (int c = 0; c < TL; c++)
-							row[c] = tmp[i * TL + c];
-						input_1d(row, o);
+						for (int q = 0; q < Q; q++)
+						{
+							f2 row[TL];
+#pragma unroll
+							for (int c = 0; c < TL; c++)
+								row[c] = tmp[q][i * TL + c];
+							input_1d(row, o[q]);
+						}
 #pragma unroll
 						for (int j = 0; j < TL; j++)
 						{
-							store_pair<MT>(dst, o[j]);
+							f2 out[Q];
+#pragma unroll
+							for (int q = 0; q < Q; q++)
+								out[q] = o[q][j];
+							store_pairs<MT, Q>(dst, out);
 							dst += plane_stride;
 						}
 					}

@@ -438,16 +438,28 @@ namespace
 			static constexpr CUtensorMapDataType value = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
 	};
 
-	template<int TS, typename T, typename MT>
-	avStatus_t launch_f43_input(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
+	/* AVOCADO_B200_INPUT_PAIRS=1 keeps one pair of channels per lane in the F(2x2) input transform (for A/B timing) */
+	bool wide_lanes_enabled()
+	{
+		static const bool enabled = []()
+		{
+			const char *env = std::getenv("AVOCADO_B200_INPUT_PAIRS");
+			return not (env != nullptr and std::strcmp(env, "1") == 0);
+		}();
+		return enabled;
+	}
+
+	template<int TS, typename T, typename MT, int Q>
+	avStatus_t launch_f43_input_q(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
 			int *deviceStatus, const bk::WeightRide *ride, bool *rideTaken)
 	{
 		if (cuda_sm_version(ctx.device) != 100 or not config.paddingValueIsZero())
 			return AVOCADO_STATUS_NOT_SUPPORTED;
-		if ((geo.channels * sizeof(T)) % 16 != 0 or not aligned_to(xPtr, 16) or not aligned_to(matricesPtr, 2 * sizeof(MT)))
+		if ((geo.channels * sizeof(T)) % 16 != 0 or not aligned_to(xPtr, 16) or not aligned_to(matricesPtr, 2 * Q * sizeof(MT)))
 			return AVOCADO_STATUS_NOT_SUPPORTED;
+		constexpr int kWarpChannels = f43::kChannelBlock * Q; /* channels one warp covers */
 		/* a strip's halo box is at most 48 KB; F(4x4) strips hold at most 8 tiles (one per warp), F(2x2) strips up to 32 */
-		const int max_pixels = 48 * 1024 / (f43::kChannelBlock * static_cast<int>(sizeof(T)));
+		const int max_pixels = 48 * 1024 / (kWarpChannels * static_cast<int>(sizeof(T)));
 		const int max_tiles = (TS == 4) ? 8 : 32;
 		const int max_tw = std::min((TS == 4) ? 8 : 16, (max_pixels / (TS + 2) - 2) / TS);
 		const int segments = (geo.tiles_w + max_tw - 1) / max_tw;
@@ -466,8 +478,8 @@ namespace
 		g.pad_w = geo.pad_w;
 		g.row_groups = (geo.tiles_h + g.strip_tiles_h - 1) / g.strip_tiles_h;
 		g.w_segments = (geo.tiles_w + g.strip_tiles_w - 1) / g.strip_tiles_w;
-		g.c_blocks = (geo.channels + f43::kChannelBlock - 1) / f43::kChannelBlock;
-		g.stage_bytes = box_h * g.box_w * f43::kChannelBlock * static_cast<int>(sizeof(T));
+		g.c_blocks = (geo.channels + kWarpChannels - 1) / kWarpChannels;
+		g.stage_bytes = box_h * g.box_w * kWarpChannels * static_cast<int>(sizeof(T));
 		g.nb_tiles = geo.nb_tiles();
 		const long long items = static_cast<long long>(geo.batch) * g.row_groups * g.w_segments * g.c_blocks;
 		if (items > 0x7FFFFFFFll)
@@ -479,11 +491,11 @@ namespace
 				static_cast<uint64_t>(geo.batch) };
 		const uint64_t strides[3] = { static_cast<uint64_t>(geo.channels) * sizeof(T), static_cast<uint64_t>(geo.width) * geo.channels * sizeof(T),
 				static_cast<uint64_t>(geo.height) * geo.width * geo.channels * sizeof(T) };
-		const uint32_t box[4] = { static_cast<uint32_t>(f43::kChannelBlock), static_cast<uint32_t>(g.box_w), static_cast<uint32_t>(box_h), 1u };
+		const uint32_t box[4] = { static_cast<uint32_t>(kWarpChannels), static_cast<uint32_t>(g.box_w), static_cast<uint32_t>(box_h), 1u };
 		if (not umma::make_tensor_map(&map, TmaType<T>::value, 4, const_cast<void*>(xPtr), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 
-		auto kernel = f43::kernel_input_tma<TS, T, MT>;
+		auto kernel = f43::kernel_input_tma<TS, T, MT, Q>;
 		constexpr int ring_bytes = 96 * 1024; /* shared memory per block for the halo ring: two blocks per SM stay resident */
 		g.stages = std::max(2, std::min(f43::kMaxStages, ring_bytes / g.stage_bytes));
 		const int smem_bytes = g.stages * g.stage_bytes + 128;
@@ -518,6 +530,24 @@ namespace
 		if (rideTaken != nullptr)
 			rideTaken[0] = job.ctas > 0;
 		return checkForErrors();
+	}
+
+	template<int TS, typename T, typename MT>
+	avStatus_t launch_f43_input(ContextObject &ctx, const ConvolutionObject &config, const ConvGeometry &geo, const void *xPtr, void *matricesPtr,
+			int *deviceStatus, const bk::WeightRide *ride, bool *rideTaken)
+	{
+		/* two pairs of channels per lane where a tile is small enough for the registers (F(2x2), 16-bit activations) and the
+		 * layer has whole groups of four channels, at least a warp's worth of them */
+		if constexpr (TS == 2 and sizeof(T) == 2)
+		{
+			if (wide_lanes_enabled() and geo.channels % 4 == 0 and geo.channels >= 2 * f43::kChannelBlock and aligned_to(matricesPtr, 4 * sizeof(MT)))
+			{
+				const avStatus_t status = launch_f43_input_q<TS, T, MT, 2>(ctx, config, geo, xPtr, matricesPtr, deviceStatus, ride, rideTaken);
+				if (status != AVOCADO_STATUS_NOT_SUPPORTED)
+					return status;
+			}
+		}
+		return launch_f43_input_q<TS, T, MT, 1>(ctx, config, geo, xPtr, matricesPtr, deviceStatus, ride, rideTaken);
 	}
 
 	f43::PlaneGeometry plane_geometry(const ConvGeometry &geo)
