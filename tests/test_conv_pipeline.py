@@ -90,6 +90,31 @@ def test_one_call_convolution_small(ctx, entry, dtype):
     assert o.error_metrics(got, ref)["elem"] <= common.TOLERANCE[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(3, 16, 16, 64, 64),     # 192 tiles: two blocks, the second half full
+                                   (5, 14, 18, 128, 72),    # 315 tiles: three blocks, the last one partial; filters end inside a block
+                                   (1, 20, 22, 72, 136),    # 110 tiles: less than one block; partial channel block, three filter blocks
+                                   (9, 13, 15, 40, 24)])    # 504 tiles (ragged edges): four blocks, fewer filters than half a block
+def test_one_call_winograd_block_edges(ctx, dtype, shape):
+    """the one-call F(2x2,3x3) convolution at the edges of its contraction + output kernel's blocks (128 tiles x 64 filters x
+    64 channels): odd block counts, partial tile, filter and channel blocks, every epilogue term"""
+    n, h, w, c, k = shape
+    d = pipeline.DirectConvolution(ctx, n, h, w, c, k, dtype)
+    x = d.x.upload(ctx, common.uniform("x", d.x.shape))
+    wt = d.wt.upload(ctx, common.he_normal_weights(k, 3, c))
+    b = d.set_bias(common.uniform("b", (k,), -0.1, 0.1))
+    d.winograd_fused(activation="relu")
+    bound = 1e-2 if dtype == "float16" else 4e-2  # bfloat16 tensors, float16 transform domain
+    assert o.error_metrics(d.y.download(ctx), o.conv2d_forward(x, wt, bias=b, activation="relu"))["elem"] <= bound
+    z = d.set_z(common.uniform("z", d.y.shape))
+    y0 = d.y.upload(ctx, common.uniform("y", d.y.shape))
+    d.winograd_fused(alpha1=1.1, alpha2=1.2, beta=0.1, activation="tanh")
+    f = lambda v: float(np.float32(v))
+    ref = o.conv2d_forward(x, wt, bias=b, z=z, y=y0, alpha1=f(1.1), alpha2=f(1.2), beta=f(0.1), activation="tanh")
+    assert o.error_metrics(d.y.download(ctx), ref)["elem"] <= bound
+    assert ctx.last_device_status() == 0
+
+
 def test_config3_shape_fused_bf16(ctx):
     """cfg 3 geometry at reduced batch: bf16, bias + ReLU"""
     n, h, w, c, k = 4, 28, 28, 128, 128
