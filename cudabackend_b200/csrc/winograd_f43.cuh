@@ -260,8 +260,12 @@ namespace f43
 	constexpr int kChannelBlock = 64; /* channels per strip and pair of a lane: one warp, two channels per lane and pair */
 	constexpr int kThreads = 256;
 	constexpr int kMaxStages = 4;
+/* Resident blocks per SM of the output transform with 16-bit transform-domain tensors.  Four (64 registers, no spills in
+ * the linear and relu forms) against three: the kernel timed alone is slower (17.0 against 15.8 us on 64 x 56 x 56 x 64
+ * float16), the pipeline it closes is faster (49.0 against 50.2 us per step), because its blocks then start on the SMs the
+ * contraction kernel frees first and find the products in L2.  Five spill 130 bytes per thread. */
 #ifndef F43_OUT_BLOCKS
-#define F43_OUT_BLOCKS 3
+#define F43_OUT_BLOCKS 4
 #endif
 
 	/* A weight transform that rides along with an input-transform launch: the first `ctas` blocks of the grid compute
