@@ -193,6 +193,15 @@ namespace
 	constexpr int kBlockM = 128;
 	constexpr int kBlockK = 64; /* elements: 128 bytes of a 16-bit type */
 	constexpr int kTcThreads = 192;
+/* Stages and epilogue buffers of the 64-column configuration.  Two stages and one buffer (65 KB: three blocks per SM)
+ * against three and two (105 KB: two blocks per SM), measured on 36 x [12544 x 64] x [64 x 64] float16: 20.9 against 21.3 us
+ * alone, 48.6 against 48.9 us for the Winograd step around it; four stages (one block per SM) 23.1 / 54.6 us. */
+#ifndef GEMM64_STAGES
+#define GEMM64_STAGES 2
+#endif
+#ifndef GEMM64_EPI
+#define GEMM64_EPI 1
+#endif
 
 	template<int BLOCK_N, int STAGES, int EPI_BUFS>
 	struct TcConfig
@@ -470,7 +479,8 @@ namespace
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		int sms = 148;
 		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx.device);
-		const int ctasPerSm = (Cfg::kSmemBytes <= 110 * 1024 and Cfg::kTmemColumns <= 256) ? 2 : 1;
+		/* as many blocks per SM as TMEM (512 columns) and shared memory (1 KB reserved per block) allow */
+		const int ctasPerSm = std::max(1, std::min(512 / Cfg::kTmemColumns, (227 * 1024) / (Cfg::kSmemBytes + 1024)));
 		const int grid = static_cast<int>(std::min<long long>(tiles, static_cast<long long>(sms) * ctasPerSm));
 		const cudaError_t launched = launch_chained(kernel, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, ctx.getStream(), mapA, mapB, mapC, mBlocks,
 				nBlocks, kBlocks, static_cast<int>(tiles), s.N, alpha, deviceStatus);
@@ -564,7 +574,7 @@ namespace
 		switch (blockN)
 		{
 			case 64:
-				return bf16 ? launch_tc_config<64, 3, 2, true>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus) : launch_tc_config<64, 3, 2, false>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus);
+				return bf16 ? launch_tc_config<64, GEMM64_STAGES, GEMM64_EPI, true>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus) : launch_tc_config<64, GEMM64_STAGES, GEMM64_EPI, false>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus);
 			case 128:
 				return bf16 ? launch_tc_config<128, 3, 2, true>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus) : launch_tc_config<128, 3, 2, false>(ctx, s, mapA, mapB, mapC, alpha, deviceStatus);
 			default:
