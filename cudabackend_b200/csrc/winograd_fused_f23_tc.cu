@@ -28,6 +28,7 @@
 #include "winograd_tables.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace
 {
@@ -64,6 +65,7 @@ namespace
 			int tiles, filters, channels;
 			int tiles_h, tiles_w, height, width;
 			int filter_blocks, channel_blocks, num_items;
+			int last_tile_block; /* items walk the blocks of tiles from this one down to the first */
 			const float *bias;
 			const void *z;
 			void *y;
@@ -244,7 +246,7 @@ namespace
 				for (int item = blockIdx.x; item < p.num_items and ok; item += gridDim.x)
 				{
 					const int fb = item % p.filter_blocks;
-					const int tb = item / p.filter_blocks;
+					const int tb = p.last_tile_block - item / p.filter_blocks;
 					/* plain nested counters: this thread's own instruction latency bounds how fast stages can be issued, and an
 					 * integer division costs it more than the copy it is about to start */
 					for (int nu = 0; nu < 4 and ok; nu++)
@@ -346,7 +348,7 @@ namespace
 			for (int item = blockIdx.x; item < p.num_items and ok; item += gridDim.x)
 			{
 				const int fb = item % p.filter_blocks;
-				const int tb = item / p.filter_blocks;
+				const int tb = p.last_tile_block - item / p.filter_blocks;
 				/* the bias of this filter block, staged once per change of block (read after the fourth group) */
 				if (staged_fb != fb)
 				{
@@ -593,6 +595,9 @@ namespace bk
 		if (items > 0x7FFFFFFFll)
 			return AVOCADO_STATUS_NOT_SUPPORTED;
 		p.num_items = static_cast<int>(items);
+		/* the input transform wrote V front to back: its last blocks of tiles are the ones still in L2 (57.6 -> 56.9 us for the
+		 * call on the 128 x 28 x 28 x 128 layer against walking them first to last) */
+		p.last_tile_block = static_cast<int>(items / p.filter_blocks) - 1;
 		p.bias = reinterpret_cast<const float*>(args.bias);
 		p.z = args.z;
 		p.y = args.y;
